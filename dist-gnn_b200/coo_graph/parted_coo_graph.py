@@ -155,14 +155,11 @@ class Parted_COO_Graph(BasicGraph):
         self.local_labels = self.labels[n * rank:n * (rank + 1)]
         self.local_train_mask = self.train_mask[n * rank:n * (rank + 1)].bool()
         self.adj_parts = graph_utils.sparse_2d_split(self.adj, n, split_dim=1)
-        self._plans = {}
 
     def plan(self, s):
-        """Device CSR plan of ``adj_parts[s]``, built on first use and owned by this graph object."""
-        if s not in self._plans:
-            import spmm_cpp
-            self._plans[s] = spmm_cpp.SpmmPlan.from_coo(self.adj_parts[s])
-        return self._plans[s]
+        """Device CSR plan of ``adj_parts[s]``, built on first use and cached for the life of that block."""
+        import spmm_cpp
+        return spmm_cpp.plan_for(self.adj_parts[s])
 
     def __repr__(self):
         return super().__repr__() + f'<Local: {self.rank}, |V|: {self.local_num_nodes}, |E|: {self.local_num_edges}>'

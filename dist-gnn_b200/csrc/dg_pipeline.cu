@@ -1,0 +1,259 @@
+// NCCL communicators and the pipelined broadcast-SpMM stage loop.
+//
+// Replaces the stage loop of the reference (light_dist_gnn/models/gcn.py:16-30): there every stage is
+// synchronize -> dist.broadcast -> synchronize -> spmm -> synchronize on one stream.  Here the broadcasts of all
+// stages are enqueued on a side stream, the local products on the compute stream, and CUDA events tie stage s's
+// product to stage s's broadcast and stage s+nbuf's broadcast to stage s's product (receive-buffer reuse), so the
+// transfer of stage s+1 crosses NVLink while stage s multiplies.  The host never blocks.
+// The 1.5D variant (1D_CAGNET/dist_15d.py:61-106) is the same loop inside the column communicator followed by a
+// sum of the partial result over the replication (row) communicator.
+#include <nccl.h>
+#include <cstring>
+#include <new>
+#include <vector>
+#include "dg_internal.h"
+
+#define DG_NCCL(expr)                                                  \
+    do {                                                               \
+        ncclResult_t _r = (expr);                                      \
+        if (_r != ncclSuccess) return DG_NCCL_ERROR_BASE + (int)_r;    \
+    } while (0)
+
+struct dg_comm {
+    ncclComm_t comm;
+    int rank, nranks, device;
+    cudaStream_t side;                       // broadcasts run here
+    cudaEvent_t ev_input;                    // this rank's block is ready on the compute stream
+    std::vector<cudaEvent_t> ev_arrived;     // per receive buffer: broadcast into it finished
+    std::vector<cudaEvent_t> ev_free;        // per receive buffer: the product that read it finished
+    std::vector<cudaEvent_t> t_comm, t_spmm; // timing pairs per stage (2 events each)
+    cudaEvent_t t_begin, t_end;
+    int timed_stages;
+};
+
+namespace {
+
+int make_events(std::vector<cudaEvent_t>& v, size_t count, unsigned flags)
+{
+    while (v.size() < count) {
+        cudaEvent_t e;
+        DG_CUDA(cudaEventCreateWithFlags(&e, flags));
+        v.push_back(e);
+    }
+    return DG_OK;
+}
+
+int finish_comm(ncclComm_t nc, dg_comm** out)
+{
+    dg_comm* c = new (std::nothrow) dg_comm();
+    if (!c) return (int)cudaErrorMemoryAllocation;
+    c->comm = nc;
+    c->timed_stages = 0;
+    DG_NCCL(ncclCommUserRank(nc, &c->rank));
+    DG_NCCL(ncclCommCount(nc, &c->nranks));
+    DG_NCCL(ncclCommCuDevice(nc, &c->device));
+    int prio_low = 0, prio_high = 0;   // highest priority: the few CTAs of a broadcast must not queue behind a product's grid
+    DG_CUDA(cudaDeviceGetStreamPriorityRange(&prio_low, &prio_high));
+    DG_CUDA(cudaStreamCreateWithPriority(&c->side, cudaStreamNonBlocking, prio_high));
+    DG_CUDA(cudaEventCreateWithFlags(&c->ev_input, cudaEventDisableTiming));
+    DG_CUDA(cudaEventCreate(&c->t_begin));
+    DG_CUDA(cudaEventCreate(&c->t_end));
+    *out = c;
+    return DG_OK;
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) { cudaGetDevice(&prev); if (prev != dev) cudaSetDevice(dev); else prev = -1; }
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+int check_loop_args(int32_t n_stages, const int32_t* roots, const dg_plan* const* plans, const float* const* vals,
+                    const float* x_local, int32_t n, int32_t F, float* const* recv, int32_t nbuf, float* z, int nranks)
+{
+    if (n_stages < 0 || n < 0 || F < 0) return DG_ERR_DIMS;
+    if (n_stages > 0 && (!roots || !plans || !vals)) return DG_ERR_NULL;
+    if ((int64_t)n * F > 0 && (!x_local || !z)) return DG_ERR_NULL;
+    for (int s = 0; s < n_stages; ++s) {
+        if (!plans[s]) return DG_ERR_NULL;
+        if (plans[s]->m != n || plans[s]->k != n) return DG_ERR_DIMS;
+        if (roots[s] < 0 || roots[s] >= nranks) return DG_ERR_DIMS;
+    }
+    if (nranks > 1) {
+        if (nbuf < 2 || !recv) return DG_ERR_DIMS;
+        for (int b = 0; b < nbuf; ++b)
+            if (!recv[b] && (int64_t)n * F > 0) return DG_ERR_NULL;
+    }
+    return DG_OK;
+}
+
+int stage_loop(dg_comm* comm, int32_t n_stages, const int32_t* roots, const dg_plan* const* plans,
+               const float* const* vals, const float* x_local, int32_t n, int32_t F, float* const* recv, int32_t nbuf,
+               float* z, int timed, cudaStream_t compute)
+{
+    const int nranks = comm ? comm->nranks : 1;
+    int rc = check_loop_args(n_stages, roots, plans, vals, x_local, n, F, recv, nbuf, z, nranks);
+    if (rc) return rc;
+    const size_t count = (size_t)n * (size_t)F;
+    if (n_stages == 0) {
+        if (count) DG_CUDA(cudaMemsetAsync(z, 0, count * sizeof(float), compute));
+        return DG_OK;
+    }
+    if (nranks == 1) {   // no collective: every stage multiplies this rank's own block
+        for (int s = 0; s < n_stages; ++s) {
+            rc = dg_spmm_csr(plans[s], vals[s], x_local, F, z, F, F, 1.f, s ? 1.f : 0.f, 0u, nullptr, nullptr, compute);
+            if (rc) return rc;
+        }
+        return DG_OK;
+    }
+    DeviceGuard guard(comm->device);
+    if ((rc = make_events(comm->ev_arrived, (size_t)nbuf, cudaEventDisableTiming))) return rc;
+    if ((rc = make_events(comm->ev_free, (size_t)nbuf, cudaEventDisableTiming))) return rc;
+    comm->timed_stages = 0;
+    if (timed) {
+        if ((rc = make_events(comm->t_comm, 2 * (size_t)n_stages, cudaEventDefault))) return rc;
+        if ((rc = make_events(comm->t_spmm, 2 * (size_t)n_stages, cudaEventDefault))) return rc;
+        DG_CUDA(cudaEventRecord(comm->t_begin, compute));
+    }
+    // Everything already queued on the compute stream (the producer of x_local, earlier readers of recv[]) comes first.
+    DG_CUDA(cudaEventRecord(comm->ev_input, compute));
+    DG_CUDA(cudaStreamWaitEvent(comm->side, comm->ev_input, 0));
+    for (int s = 0; s < n_stages; ++s) {
+        const int b = s % nbuf;
+        const bool is_root = roots[s] == comm->rank;
+        float* landing = is_root ? const_cast<float*>(x_local) : recv[b];
+        if (!is_root && s >= nbuf) DG_CUDA(cudaStreamWaitEvent(comm->side, comm->ev_free[b], 0));
+        if (timed) DG_CUDA(cudaEventRecord(comm->t_comm[2 * s], comm->side));
+        if (count) DG_NCCL(ncclBroadcast(x_local, landing, count, ncclFloat, roots[s], comm->comm, comm->side));
+        if (timed) DG_CUDA(cudaEventRecord(comm->t_comm[2 * s + 1], comm->side));
+        DG_CUDA(cudaEventRecord(comm->ev_arrived[b], comm->side));
+        DG_CUDA(cudaStreamWaitEvent(compute, comm->ev_arrived[b], 0));
+        if (timed) DG_CUDA(cudaEventRecord(comm->t_spmm[2 * s], compute));
+        rc = dg_spmm_csr(plans[s], vals[s], landing, F, z, F, F, 1.f, s ? 1.f : 0.f, 0u, nullptr, nullptr, compute);
+        if (rc) return rc;
+        if (timed) DG_CUDA(cudaEventRecord(comm->t_spmm[2 * s + 1], compute));
+        DG_CUDA(cudaEventRecord(comm->ev_free[b], compute));
+    }
+    if (timed) {
+        DG_CUDA(cudaEventRecord(comm->t_end, compute));
+        comm->timed_stages = n_stages;
+    }
+    return DG_OK;
+}
+
+}  // namespace
+
+extern "C" int dg_comm_unique_id(char host_id_out[128])
+{
+    if (!host_id_out) return DG_ERR_NULL;
+    static_assert(sizeof(ncclUniqueId) == 128, "ncclUniqueId is expected to be 128 bytes");
+    ncclUniqueId id;
+    DG_NCCL(ncclGetUniqueId(&id));
+    memcpy(host_id_out, &id, sizeof(id));
+    return DG_OK;
+}
+
+extern "C" int dg_comm_create(const char host_id[128], int rank, int nranks, dg_comm** out)
+{
+    if (!host_id || !out) return DG_ERR_NULL;
+    if (nranks < 1 || rank < 0 || rank >= nranks) return DG_ERR_DIMS;
+    *out = nullptr;
+    ncclUniqueId id;
+    memcpy(&id, host_id, sizeof(id));
+    ncclComm_t nc;
+    DG_NCCL(ncclCommInitRank(&nc, nranks, id, rank));
+    return finish_comm(nc, out);
+}
+
+extern "C" int dg_comm_split(dg_comm* parent, int color, int key, dg_comm** out)
+{
+    if (!parent || !out) return DG_ERR_NULL;
+    *out = nullptr;
+    DeviceGuard guard(parent->device);
+    ncclComm_t nc = nullptr;
+    DG_NCCL(ncclCommSplit(parent->comm, color < 0 ? NCCL_SPLIT_NOCOLOR : color, key, &nc, nullptr));
+    if (!nc) return DG_OK;    // this rank asked to stay out
+    return finish_comm(nc, out);
+}
+
+extern "C" int dg_comm_destroy(dg_comm* c)
+{
+    if (!c) return DG_OK;
+    DeviceGuard guard(c->device);
+    cudaStreamSynchronize(c->side);
+    ncclCommDestroy(c->comm);
+    for (auto* v : {&c->ev_arrived, &c->ev_free, &c->t_comm, &c->t_spmm})
+        for (cudaEvent_t e : *v) cudaEventDestroy(e);
+    cudaEventDestroy(c->ev_input);
+    cudaEventDestroy(c->t_begin);
+    cudaEventDestroy(c->t_end);
+    cudaStreamDestroy(c->side);
+    delete c;
+    return DG_OK;
+}
+
+extern "C" int dg_comm_rank(const dg_comm* c, int* rank, int* nranks)
+{
+    if (!c) return DG_ERR_NULL;
+    if (rank) *rank = c->rank;
+    if (nranks) *nranks = c->nranks;
+    return DG_OK;
+}
+
+extern "C" int dg_comm_allreduce_sum(dg_comm* c, float* buf, int64_t count, void* stream)
+{
+    if (!c || (!buf && count > 0)) return DG_ERR_NULL;
+    if (count < 0) return DG_ERR_DIMS;
+    if (count == 0 || c->nranks == 1) return DG_OK;
+    DeviceGuard guard(c->device);
+    DG_NCCL(ncclAllReduce(buf, buf, (size_t)count, ncclFloat, ncclSum, c->comm, (cudaStream_t)stream));
+    return DG_OK;
+}
+
+extern "C" int dg_comm_broadcast(dg_comm* c, float* buf, int64_t count, int root, void* stream)
+{
+    if (!c || (!buf && count > 0)) return DG_ERR_NULL;
+    if (count < 0 || root < 0 || root >= c->nranks) return DG_ERR_DIMS;
+    if (count == 0 || c->nranks == 1) return DG_OK;
+    DeviceGuard guard(c->device);
+    DG_NCCL(ncclBroadcast(buf, buf, (size_t)count, ncclFloat, root, c->comm, (cudaStream_t)stream));
+    return DG_OK;
+}
+
+extern "C" int dg_bcast_spmm_1d(dg_comm* comm, int32_t n_stages, const int32_t* roots, const dg_plan* const* plans,
+                                const float* const* vals, const float* x_local, int32_t n, int32_t F,
+                                float* const* recv, int32_t nbuf, float* z, int timed, void* compute_stream)
+{
+    return stage_loop(comm, n_stages, roots, plans, vals, x_local, n, F, recv, nbuf, z, timed, (cudaStream_t)compute_stream);
+}
+
+extern "C" int dg_bcast_spmm_15d(dg_comm* col_comm, dg_comm* row_comm, int32_t n_stages, const int32_t* roots,
+                                 const dg_plan* const* plans, const float* const* vals, const float* x_local,
+                                 int32_t n, int32_t F, float* const* recv, int32_t nbuf, float* z, int timed,
+                                 void* compute_stream)
+{
+    int rc = stage_loop(col_comm, n_stages, roots, plans, vals, x_local, n, F, recv, nbuf, z, timed, (cudaStream_t)compute_stream);
+    if (rc) return rc;
+    if (row_comm) rc = dg_comm_allreduce_sum(row_comm, z, (int64_t)n * F, compute_stream);
+    return rc;
+}
+
+extern "C" int dg_comm_last_times(dg_comm* c, dg_stage_times* out)
+{
+    if (!c || !out) return DG_ERR_NULL;
+    *out = dg_stage_times{0.f, 0.f, 0.f, 0};
+    if (c->timed_stages == 0) return DG_OK;
+    DeviceGuard guard(c->device);
+    DG_CUDA(cudaEventSynchronize(c->t_end));
+    DG_CUDA(cudaStreamSynchronize(c->side));
+    for (int s = 0; s < c->timed_stages; ++s) {
+        float ms = 0.f;
+        DG_CUDA(cudaEventElapsedTime(&ms, c->t_comm[2 * s], c->t_comm[2 * s + 1]));
+        out->comm_ms += ms;
+        DG_CUDA(cudaEventElapsedTime(&ms, c->t_spmm[2 * s], c->t_spmm[2 * s + 1]));
+        out->spmm_ms += ms;
+    }
+    DG_CUDA(cudaEventElapsedTime(&out->total_ms, c->t_begin, c->t_end));
+    out->stages = c->timed_stages;
+    return DG_OK;
+}

@@ -1,0 +1,135 @@
+"""Process-group set-up and collective helpers with the surface of light_dist_gnn/dist_utils/env.py:10-54, plus the
+replication groups of the 1.5D variant (1D_CAGNET/utils.py:21-49).
+
+Two layers of communicators live here.  torch.distributed (NCCL or gloo) is the plumbing: rendezvous, object
+exchange, the occasional all-gather of outputs for evaluation.  The hot path - the broadcasts of the stage loop,
+the dW all-reduce and the 1.5D partial-sum all-reduce - runs on the library's own NCCL communicators
+(``spmm_cpp.Comm``) created here when the ranks own CUDA devices.
+
+Differences from the reference, on purpose: one visible GPU selects that GPU (the reference falls back to the CPU
+unless it sees more than one, env.py:26-31); the O(P^2) two-rank groups of env.py:51-54, which no model of
+light_dist_gnn uses, are not created (``p2p_group_dict`` stays empty); the timer's side channel is the process
+group's own store instead of a fixed file under the temp folder, which went stale between runs.
+"""
+import os
+
+import torch
+import torch.distributed as dist
+
+from . import schedule
+from .logger import DistLogger
+from .timer import DistTimer
+
+
+class DistEnv:
+    env = None
+
+    def __init__(self, rank, world_size, backend='nccl', rep=1):
+        assert rank >= 0
+        assert world_size > 0
+        schedule.check_layout(world_size, rep)
+        self.rank, self.world_size, self.backend, self.rep = rank, world_size, backend, rep
+        self.rank_grp, self.rank_col = rank // rep, rank % rep          # row block, replica index
+        self.init_device()
+        self.init_dist_groups()
+        self.init_comms()
+        self.logger = DistLogger(self)
+        self.timer = DistTimer(self)
+        self.store = dist.PrefixStore('dist_gnn_timer', dist.distributed_c10d._get_default_store())
+        self._recv = {}
+        DistEnv.env = self
+
+    def __repr__(self):
+        return '<DistEnv %d/%d %s>' % (self.rank, self.world_size, self.backend)
+
+    def init_device(self):
+        if torch.cuda.is_available() and self.backend == 'nccl':
+            local = int(os.environ.get('LOCAL_RANK', self.rank)) % torch.cuda.device_count()
+            self.device = torch.device('cuda', local)
+            torch.cuda.set_device(self.device)
+        else:
+            self.device = torch.device('cpu')
+
+    def init_dist_groups(self):
+        if not dist.is_initialized():
+            dist.init_process_group(backend=self.backend, rank=self.rank, world_size=self.world_size, init_method='env://')
+        self.world_group = dist.new_group(list(range(self.world_size)))
+        self.p2p_group_dict = {}
+        self.row_procs = schedule.row_groups(self.world_size, self.rep)
+        self.col_procs = schedule.col_groups(self.world_size, self.rep)
+        self.row_groups, self.col_groups = [self.world_group], [self.world_group]
+        if self.rep > 1:    # every rank creates every group, in the same order
+            self.row_groups = [dist.new_group(p) for p in self.row_procs]
+            self.col_groups = [dist.new_group(p) for p in self.col_procs]
+
+    def init_comms(self):
+        """Library communicators for the hot path: world, and for 1.5D the column (broadcast) and row (replica) groups."""
+        self.comm = self.col_comm = self.row_comm = None
+        if self.device.type != 'cuda' or self.world_size == 1:
+            return
+        import spmm_cpp
+        box = [spmm_cpp.Comm.unique_id() if self.rank == 0 else None]
+        dist.broadcast_object_list(box, src=0, group=self.world_group)
+        self.comm = spmm_cpp.Comm.create(box[0], self.rank, self.world_size, self.device)
+        self.col_comm = self.comm
+        if self.rep > 1:
+            self.col_comm = self.comm.split(self.rank_col, self.rank)
+            self.row_comm = self.comm.split(self.rank_grp, self.rank)
+
+    # ---- collective helpers (env.py:33-45) -------------------------------------------------------------------------
+    def all_reduce_sum(self, tensor):
+        """dW all-reduce of the layer backward: world group in 1D, column group in 1.5D."""
+        if tensor.is_cuda and self.col_comm is not None:
+            self.col_comm.all_reduce_sum(tensor)
+        elif self.world_size > 1:
+            dist.all_reduce(tensor, op=dist.ReduceOp.SUM, group=self.col_groups[self.rank_col] if self.rep > 1 else self.world_group)
+
+    def broadcast(self, tensor, src):
+        dist.broadcast(tensor, src=src, group=self.world_group)
+
+    def all_gather_then_cat(self, src_t):
+        """Row blocks of every rank stacked in block order (one replica per block in 1.5D)."""
+        if self.rep == 1:
+            group, size = self.world_group, self.world_size
+        else:
+            group, size = self.col_groups[self.rank_col], self.world_size // self.rep
+        recv_list = [torch.zeros_like(src_t) for _ in range(size)]
+        dist.all_gather(recv_list, src_t.contiguous(), group=group)
+        return torch.cat(recv_list, dim=0)
+
+    def all_gather_object(self, obj):
+        out = [None] * self.world_size
+        dist.all_gather_object(out, obj, group=self.world_group)
+        return out
+
+    def barrier_all(self):
+        if self.device.type == 'cuda':
+            dist.barrier(self.world_group, device_ids=[self.device.index])
+        else:
+            dist.barrier(self.world_group)
+
+    # ---- stage-loop support ----------------------------------------------------------------------------------------
+    def stages(self):
+        return schedule.stages(self.rank, self.world_size, self.rep)
+
+    def recv_buffers(self, n, F, nbuf=2):
+        """nbuf persistent receive buffers able to hold one n x F block, reused by every stage loop."""
+        need = n * F
+        bufs = self._recv.get(nbuf)
+        if bufs is None or bufs[0].numel() < need:
+            bufs = [torch.empty(need, dtype=torch.float32, device=self.device) for _ in range(nbuf)]
+            self._recv[nbuf] = bufs
+        return [b[:need].view(n, F) for b in bufs]
+
+    def shutdown(self):
+        for c in {id(c): c for c in (self.row_comm, self.col_comm, self.comm) if c is not None}.values():
+            c.destroy()
+        self.comm = self.col_comm = self.row_comm = None
+        if dist.is_initialized():
+            dist.destroy_process_group()
+        DistEnv.env = None
+
+
+class DistUtil:
+    def __init__(self, env):
+        self.env = env

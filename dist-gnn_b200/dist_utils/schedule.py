@@ -1,0 +1,51 @@
+"""Stage schedules of the distributed SpMM: which sparse column block a rank multiplies at each stage and which
+rank's feature block it needs for it.  Pure host logic shared by the CUDA stage loop and by the tests.
+
+1D   (light_dist_gnn/models/gcn.py:21-29): P stages, stage s multiplies column block s by the block of rank s.
+1.5D (1D_CAGNET/dist_15d.py:64-76, groups 1D_CAGNET/utils.py:36-49): P ranks = R row blocks x c replicas, rank ->
+     (row block rank // c, replica rank % c).  Replica j handles P // c^2 consecutive column blocks starting at
+     j * (P // c^2); the last replica also takes what is left.  The block of column block b comes from the rank that
+     holds row block b in the same replica column, i.e. global rank b*c + j, inside the column group {j, j+c, ...}.
+     Partial results are then summed over the row group {b*c .. b*c+c-1}.
+"""
+from collections import namedtuple
+
+Stage = namedtuple('Stage', 'part root_global root_in_group')
+
+
+def check_layout(world_size, rep):
+    if rep < 1 or world_size % rep:
+        raise ValueError(f'replication factor {rep} must divide the world size {world_size}')
+    if rep > 1 and world_size // (rep * rep) < 1:
+        raise ValueError(f'1.5D needs world_size >= rep^2 (got {world_size}, rep {rep})')
+
+
+def row_groups(world_size, rep):
+    """Replication groups: consecutive `rep` ranks share one row block."""
+    return [list(range(i, i + rep)) for i in range(0, world_size, rep)]
+
+
+def col_groups(world_size, rep):
+    """Broadcast groups: ranks with the same replica index, one per row block."""
+    return [list(range(j, world_size, rep)) for j in range(rep)]
+
+
+def data_rank(rank, rep):
+    """Row block a rank works on, and how many row blocks exist is world_size // rep."""
+    return rank // rep
+
+
+def stages_1d(world_size):
+    return [Stage(s, s, s) for s in range(world_size)]
+
+
+def stages_15d(rank, world_size, rep):
+    check_layout(world_size, rep)
+    replica = rank % rep
+    basic = world_size // (rep * rep)
+    count = basic if replica != rep - 1 else world_size // rep - (rep - 1) * basic
+    return [Stage(replica * basic + i, (replica * basic + i) * rep + replica, replica * basic + i) for i in range(count)]
+
+
+def stages(rank, world_size, rep=1):
+    return stages_1d(world_size) if rep == 1 else stages_15d(rank, world_size, rep)

@@ -1,0 +1,88 @@
+"""The distributed GCN layer and model with the surface of light_dist_gnn/models/gcn.py, running on the CUDA stage loop.
+
+``broadcast(local_adj_parts, local_feature, tag)`` computes z = sum_s A[rank, s] @ X_s like gcn.py:16-30, but hands
+the whole loop to the library (spmm_cpp.bcast_spmm): NCCL broadcasts on a side stream into two receive buffers,
+hand-written SpMM kernels on the current stream, no host synchronisation.  With ``DistEnv(..., rep=c)`` the same call
+runs the 1.5D schedule of 1D_CAGNET/dist_15d.py:61-106 (column-group broadcasts, then the sum of the partial z over
+the replication group).  ``DistGCNLayer`` keeps the reference's forward/backward algebra (gcn.py:35-53), including
+the reuse of the un-transposed row block of A in backward, which is exact only for a symmetric adjacency.
+
+There is no CPU implementation: CPU tensors raise.
+"""
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+import spmm_cpp
+from dist_utils import DistEnv
+
+
+def spmm(A, B, C):
+    """C += A @ B in place for a sparse COO block A (the binding of gcn.py:9-13, on a cached plan)."""
+    spmm_cpp.plan_for(A).spmm(B, C, 1.0, 1.0)
+    return C
+
+
+def broadcast(local_adj_parts, local_feature, tag):
+    env = DistEnv.env
+    if not local_feature.is_cuda:
+        raise RuntimeError('the broadcast-SpMM stage loop runs on CUDA tensors only; there is no CPU path')
+    x = local_feature.contiguous()
+    n, width = x.shape
+    stages = env.stages()
+    plans = [spmm_cpp.plan_for(local_adj_parts[st.part]) for st in stages]
+    z = torch.empty_like(x)
+    comm = env.col_comm
+    recv = env.recv_buffers(n, width) if comm is not None else None
+    with env.timer.timing_cuda('broadcast+spmm'):
+        spmm_cpp.bcast_spmm(comm, [st.root_in_group for st in stages], plans, x, recv, z, row_comm=env.row_comm)
+    return z
+
+
+class DistGCNLayer(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, features, weight, adj_parts, tag):
+        ctx.save_for_backward(features, weight)
+        ctx.adj_parts, ctx.tag = adj_parts, tag
+        z_local = broadcast(adj_parts, features, 'Forward' + tag)
+        with DistEnv.env.timer.timing_cuda('mm'):
+            z_local = torch.mm(z_local, weight)
+        return z_local
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        features, weight = ctx.saved_tensors
+        ag = broadcast(ctx.adj_parts, grad_output, 'Backward' + ctx.tag)
+        with DistEnv.env.timer.timing_cuda('mm'):
+            grad_features = torch.mm(ag, weight.t()) if ctx.needs_input_grad[0] else None
+            grad_weight = torch.mm(features.t(), ag)
+        with DistEnv.env.timer.timing_cuda('all_reduce'):
+            DistEnv.env.all_reduce_sum(grad_weight)
+        return grad_features, grad_weight, None, None
+
+
+class GCN(nn.Module):
+    """num_layers DistGCNLayers with ReLU between them, no bias (gcn.py:56-72).  Weights are drawn as the reference
+    draws them - torch.rand on the host after manual_seed(0), layer by layer - unless `weights` injects them."""
+
+    def __init__(self, g, env, hidden_dim=16, num_layers=3, weights=None):
+        super().__init__()
+        self.g, self.env, self.num_layers = g, env, num_layers
+        in_dim, out_dim = g.features.size(1), g.num_classes
+        dims = [in_dim] + [hidden_dim] * (num_layers - 1) + [out_dim]
+        torch.manual_seed(0)
+        for l in range(num_layers):
+            w = torch.rand(dims[l], dims[l + 1]) if weights is None else weights[l].detach().clone().float()
+            assert tuple(w.shape) == (dims[l], dims[l + 1])
+            setattr(self, f'weight{l + 1}', nn.Parameter(w.to(env.device)))
+
+    def weights(self):
+        return [getattr(self, f'weight{l + 1}') for l in range(self.num_layers)]
+
+    def forward(self, features):
+        h = features
+        for l, w in enumerate(self.weights()):
+            h = DistGCNLayer.apply(h, w, self.g.adj_parts, f'L{l + 1}')
+            if l < self.num_layers - 1:
+                h = F.relu(h)
+        return h

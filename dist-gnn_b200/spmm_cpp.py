@@ -1,0 +1,280 @@
+"""Python face of libdist_gnn_b200.so, under the module name the reference imports (``spmm_cpp``).
+
+``spmm_cusparse(row, col, val, A_row, A_col, B, C, alpha, beta)`` keeps the nine-argument signature of the
+reference's pybind module (light_dist_gnn/spmm_cpp/spmm.cpp:17, :35-37) and updates C in place, so
+``from spmm_cpp import spmm_cusparse`` in light_dist_gnn/models/gcn.py:10 binds to the hand-written sm_100a kernels.
+Everything goes through the C ABI of include/dist_gnn_b200.h with raw device pointers (ctypes); torch only owns
+the memory and the streams.  There is no CPU implementation behind any of these calls: without the library or
+without CUDA tensors they raise.
+"""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, 'csrc', 'libdist_gnn_b200.so')
+_lib = None
+
+EPI_ROW_SCALE, EPI_BIAS, EPI_RELU = 1, 2, 4
+
+
+class PlanStats(ctypes.Structure):
+    _fields_ = [('nnz', ctypes.c_int64), ('m', ctypes.c_int32), ('k', ctypes.c_int32),
+                ('heavy_threshold', ctypes.c_int32), ('chunk', ctypes.c_int32),
+                ('heavy_rows', ctypes.c_int32), ('heavy_chunks', ctypes.c_int32),
+                ('heavy_nnz', ctypes.c_int64), ('max_row_nnz', ctypes.c_int64), ('touched_columns', ctypes.c_int64)]
+
+
+class StageTimes(ctypes.Structure):
+    _fields_ = [('comm_ms', ctypes.c_float), ('spmm_ms', ctypes.c_float), ('total_ms', ctypes.c_float),
+                ('stages', ctypes.c_int32)]
+
+
+class Profile(ctypes.Structure):
+    _fields_ = [('spmm_ms', ctypes.c_double), ('alg_bytes', ctypes.c_double), ('gather_bytes', ctypes.c_double),
+                ('flops', ctypes.c_double), ('products', ctypes.c_int64), ('kernel_launches', ctypes.c_int64)]
+
+
+def lib():
+    """The loaded C library; raises if it has not been built (python dist-gnn_b200/csrc/build.py)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise RuntimeError(f'{_LIB_PATH} is missing: build it with `python dist-gnn_b200/csrc/build.py`; '
+                               'there is no fallback implementation')
+        L = ctypes.CDLL(_LIB_PATH)
+        vp, i32, i64, f32, u32 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_float, ctypes.c_uint32
+        pp = ctypes.POINTER(ctypes.c_void_p)
+        sig = {
+            'dg_strerror': ([ctypes.c_int], ctypes.c_char_p),
+            'dg_version': ([], ctypes.c_int),
+            'dg_plan_create': ([vp, vp, i64, i32, i32, vp, pp], ctypes.c_int),
+            'dg_plan_create_ex': ([vp, vp, i64, i32, i32, i32, i32, vp, pp], ctypes.c_int),
+            'dg_plan_destroy': ([vp], ctypes.c_int),
+            'dg_plan_get_stats': ([vp, ctypes.POINTER(PlanStats)], ctypes.c_int),
+            'dg_plan_copy_rowptr': ([vp, vp, vp], ctypes.c_int),
+            'dg_spmm_csr': ([vp, vp, vp, i64, vp, i64, i32, f32, f32, u32, vp, vp, vp], ctypes.c_int),
+            'dg_spmm_coo': ([vp, vp, vp, i64, i32, i32, vp, vp, i32, f32, f32, vp], ctypes.c_int),
+            'dg_comm_unique_id': ([ctypes.c_char_p], ctypes.c_int),
+            'dg_comm_create': ([ctypes.c_char_p, ctypes.c_int, ctypes.c_int, pp], ctypes.c_int),
+            'dg_comm_split': ([vp, ctypes.c_int, ctypes.c_int, pp], ctypes.c_int),
+            'dg_comm_destroy': ([vp], ctypes.c_int),
+            'dg_comm_rank': ([vp, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)], ctypes.c_int),
+            'dg_comm_allreduce_sum': ([vp, vp, i64, vp], ctypes.c_int),
+            'dg_comm_broadcast': ([vp, vp, i64, ctypes.c_int, vp], ctypes.c_int),
+            'dg_bcast_spmm_1d': ([vp, i32, vp, vp, vp, vp, i32, i32, vp, i32, vp, ctypes.c_int, vp], ctypes.c_int),
+            'dg_bcast_spmm_15d': ([vp, vp, i32, vp, vp, vp, vp, i32, i32, vp, i32, vp, ctypes.c_int, vp], ctypes.c_int),
+            'dg_comm_last_times': ([vp, ctypes.POINTER(StageTimes)], ctypes.c_int),
+            'dg_profile_begin': ([], ctypes.c_int),
+            'dg_profile_end': ([ctypes.POINTER(Profile)], ctypes.c_int),
+        }
+        for name, (argtypes, restype) in sig.items():
+            fn = getattr(L, name)
+            fn.argtypes, fn.restype = argtypes, restype
+        _lib = L
+    return _lib
+
+
+def check(code):
+    if code != 0:
+        raise RuntimeError(f'dist_gnn_b200 error {code}: {lib().dg_strerror(code).decode()}')
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dev_tensor(t, dtype, what):
+    if not (isinstance(t, torch.Tensor) and t.is_cuda):
+        raise RuntimeError(f'{what} must be a CUDA tensor: this library has no CPU path')
+    if t.dtype != dtype or not t.is_contiguous():
+        raise RuntimeError(f'{what} must be a contiguous {dtype} tensor, got {t.dtype} contiguous={t.is_contiguous()}')
+    return t
+
+
+class SpmmPlan:
+    """Device CSR plan of one sparse block (dg_plan).  Keeps the int32 column ids and fp32 values alive."""
+
+    def __init__(self, row_i32, col_i32, values, m, k, heavy_threshold=0, chunk=0):
+        _dev_tensor(row_i32, torch.int32, 'row ids'), _dev_tensor(col_i32, torch.int32, 'column ids')
+        _dev_tensor(values, torch.float32, 'values')
+        if not (row_i32.numel() == col_i32.numel() == values.numel()):
+            raise RuntimeError('row, col and value arrays differ in length')
+        self.col, self.values, self.m, self.k, self.device = col_i32, values, int(m), int(k), values.device
+        handle = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            check(lib().dg_plan_create_ex(row_i32.data_ptr(), col_i32.data_ptr(), values.numel(), self.m, self.k,
+                                          heavy_threshold, chunk, _stream(), ctypes.byref(handle)))
+        self.handle = handle
+
+    @classmethod
+    def from_coo(cls, A, heavy_threshold=0, chunk=0):
+        """From a coalesced torch sparse COO tensor on a CUDA device (int64 indices are narrowed once, here)."""
+        if not A.is_coalesced():
+            A = A.coalesce()
+        idx = A.indices()
+        if max(A.shape) >= 2**31:
+            raise RuntimeError('block dimensions must fit int32')
+        return cls(idx[0].to(torch.int32), idx[1].to(torch.int32).contiguous(), A.values().contiguous(),
+                   A.size(0), A.size(1), heavy_threshold, chunk)
+
+    def stats(self):
+        s = PlanStats()
+        check(lib().dg_plan_get_stats(self.handle, ctypes.byref(s)))
+        return {name: getattr(s, name) for name, _ in PlanStats._fields_}
+
+    def rowptr(self):
+        out = torch.empty(self.m + 1, dtype=torch.int64)
+        with torch.cuda.device(self.device):
+            check(lib().dg_plan_copy_rowptr(self.handle, out.data_ptr(), _stream()))
+        return out
+
+    def spmm(self, B, C, alpha=1.0, beta=1.0, row_scale=None, bias=None, relu=False, values=None):
+        """C <- epilogue(alpha * A @ B + beta * C) in place; B [k, F] and C [m, F] may be row-strided views."""
+        val = self.values if values is None else _dev_tensor(values, torch.float32, 'values')
+        for t, rows, what in ((B, self.k, 'B'), (C, self.m, 'C')):
+            if not (isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.float32 and t.dim() == 2):
+                raise RuntimeError(f'{what} must be a 2-D fp32 CUDA tensor')
+            if t.size(0) != rows or (t.size(1) > 1 and t.stride(1) != 1):
+                raise RuntimeError(f'{what} has shape {tuple(t.shape)} / strides {t.stride()}, expected {rows} rows, unit column stride')
+        if B.size(1) != C.size(1):
+            raise RuntimeError('B and C differ in width')
+        flags = (EPI_ROW_SCALE if row_scale is not None else 0) | (EPI_BIAS if bias is not None else 0) | (EPI_RELU if relu else 0)
+        if row_scale is not None:
+            _dev_tensor(row_scale, torch.float32, 'row_scale')
+        if bias is not None:
+            _dev_tensor(bias, torch.float32, 'bias')
+        F = B.size(1)
+        ldb = B.stride(0) if B.size(0) > 1 else max(F, 1)
+        ldc = C.stride(0) if C.size(0) > 1 else max(F, 1)
+        with torch.cuda.device(self.device):
+            check(lib().dg_spmm_csr(self.handle, val.data_ptr(), B.data_ptr(), ldb, C.data_ptr(), ldc, F, alpha, beta, flags,
+                                    row_scale.data_ptr() if row_scale is not None else None,
+                                    bias.data_ptr() if bias is not None else None, _stream()))
+        return C
+
+    def algorithmic_bytes(self, F, beta_nonzero):
+        """Compulsory HBM traffic of one product: CSR once, each touched row of B once, C written once (and read once
+        when accumulating): 8*nnz + 4*(m+1) + 4*F*touched + 4*F*m*(1 + [beta != 0]).  (The row offsets are int64
+        here, so the real compulsory figure is 4*(m+1) bytes larger; the smaller one is the one reported.)"""
+        s = self.stats()
+        return 8 * s['nnz'] + 4 * (s['m'] + 1) + 4 * F * s['touched_columns'] + 4 * F * s['m'] * (2 if beta_nonzero else 1)
+
+    def __del__(self):
+        h, self.handle = getattr(self, 'handle', None), None
+        if h and _lib is not None:
+            _lib.dg_plan_destroy(h)
+
+
+def profile_begin():
+    """Start bracketing every local product with CUDA events (dg_profile_begin)."""
+    check(lib().dg_profile_begin())
+
+
+def profile_end():
+    """Synchronise and return the summed product time, traffic models, flops and kernel-launch count."""
+    p = Profile()
+    check(lib().dg_profile_end(ctypes.byref(p)))
+    return {name: getattr(p, name) for name, _ in Profile._fields_}
+
+
+_plan_cache = {}
+
+
+def plan_for(A):
+    """The cached SpmmPlan of a sparse COO block, built on first use and dropped when the tensor dies."""
+    import weakref
+    key = id(A)
+    hit = _plan_cache.get(key)
+    if hit is not None and hit[0]() is A:
+        return hit[1]
+    plan = SpmmPlan.from_coo(A)
+    _plan_cache[key] = (weakref.ref(A, lambda _ref, key=key: _plan_cache.pop(key, None)), plan)
+    return plan
+
+
+def spmm_cusparse(A_row_idx, A_col_idx, A_values, A_row, A_col, B, C, alpha, beta):
+    """Drop-in for the reference's native op: C = alpha * A_coo @ B + beta * C, in place, on the current stream."""
+    _dev_tensor(A_row_idx, torch.int32, 'A_row_idx'), _dev_tensor(A_col_idx, torch.int32, 'A_col_idx')
+    _dev_tensor(A_values, torch.float32, 'A_values'), _dev_tensor(B, torch.float32, 'B'), _dev_tensor(C, torch.float32, 'C')
+    if B.dim() != 2 or C.dim() != 2 or B.size(0) != A_col or C.size(0) != A_row or B.size(1) != C.size(1):
+        raise RuntimeError(f'shape mismatch: A {A_row}x{A_col}, B {tuple(B.shape)}, C {tuple(C.shape)}')
+    with torch.cuda.device(C.device):
+        check(lib().dg_spmm_coo(A_row_idx.data_ptr(), A_col_idx.data_ptr(), A_values.data_ptr(), A_values.numel(),
+                                int(A_row), int(A_col), B.data_ptr(), C.data_ptr(), B.size(1), float(alpha), float(beta), _stream()))
+
+
+class Comm:
+    """One NCCL communicator with its side stream (dg_comm)."""
+
+    def __init__(self, handle, device):
+        self.handle, self.device = handle, device
+        r, n = ctypes.c_int(), ctypes.c_int()
+        check(lib().dg_comm_rank(handle, ctypes.byref(r), ctypes.byref(n)))
+        self.rank, self.size = r.value, n.value
+
+    @staticmethod
+    def unique_id():
+        buf = ctypes.create_string_buffer(128)
+        check(lib().dg_comm_unique_id(buf))
+        return buf.raw
+
+    @classmethod
+    def create(cls, unique_id, rank, size, device):
+        handle = ctypes.c_void_p()
+        with torch.cuda.device(device):
+            check(lib().dg_comm_create(unique_id, rank, size, ctypes.byref(handle)))
+        return cls(handle, device)
+
+    def split(self, color, key):
+        handle = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            check(lib().dg_comm_split(self.handle, color, key, ctypes.byref(handle)))
+        return Comm(handle, self.device) if handle.value else None
+
+    def all_reduce_sum(self, t):
+        _dev_tensor(t, torch.float32, 'tensor')
+        with torch.cuda.device(self.device):
+            check(lib().dg_comm_allreduce_sum(self.handle, t.data_ptr(), t.numel(), _stream()))
+
+    def broadcast(self, t, root):
+        _dev_tensor(t, torch.float32, 'tensor')
+        with torch.cuda.device(self.device):
+            check(lib().dg_comm_broadcast(self.handle, t.data_ptr(), t.numel(), root, _stream()))
+
+    def last_times(self):
+        s = StageTimes()
+        with torch.cuda.device(self.device):
+            check(lib().dg_comm_last_times(self.handle, ctypes.byref(s)))
+        return dict(comm_ms=s.comm_ms, spmm_ms=s.spmm_ms, total_ms=s.total_ms, stages=s.stages)
+
+    def destroy(self):
+        h, self.handle = self.handle, None
+        if h and _lib is not None:
+            _lib.dg_comm_destroy(h)
+
+
+def bcast_spmm(comm, roots, plans, x_local, recv, z, row_comm=None, timed=False):
+    """The pipelined stage loop (dg_bcast_spmm_1d / _15d): z <- sum_s plans[s] @ X_{roots[s]}.
+
+    comm is a Comm or None (single rank); recv a list of >= 2 fp32 CUDA buffers with x_local's shape."""
+    _dev_tensor(x_local, torch.float32, 'x_local'), _dev_tensor(z, torch.float32, 'z')
+    n, F = x_local.shape
+    S = len(plans)
+    roots_arr = (ctypes.c_int32 * max(S, 1))(*roots)
+    plan_arr = (ctypes.c_void_p * max(S, 1))(*[p.handle for p in plans])
+    val_arr = (ctypes.c_void_p * max(S, 1))(*[p.values.data_ptr() for p in plans])
+    recv = recv or []
+    for b in recv:
+        _dev_tensor(b, torch.float32, 'receive buffer')
+        if b.numel() < n * F:
+            raise RuntimeError('receive buffer smaller than one block')
+    recv_arr = (ctypes.c_void_p * max(len(recv), 1))(*[b.data_ptr() for b in recv])
+    args = (S, roots_arr, plan_arr, val_arr, x_local.data_ptr(), n, F, recv_arr, len(recv), z.data_ptr(), int(timed), _stream())
+    with torch.cuda.device(x_local.device):
+        if row_comm is None:
+            check(lib().dg_bcast_spmm_1d(comm.handle if comm else None, *args))
+        else:
+            check(lib().dg_bcast_spmm_15d(comm.handle if comm else None, row_comm.handle, *args))
+    return z

@@ -1,0 +1,153 @@
+/*
+ * dist_gnn_b200 - C ABI of the B200 (sm_100a) broadcast-SpMM library.
+ *
+ * This is the boundary a binding of the reference project talks to: plain pointers and sizes, no
+ * framework types.  It replaces, for the 1D / 1.5D broadcast-based distributed SpMM of
+ * light_dist_gnn, (a) the cuSPARSE wrapper spmm_cusparse (light_dist_gnn/spmm_cpp/spmm.cpp:17-33) and
+ * (b) the per-stage torch.distributed.broadcast + spmm loop (light_dist_gnn/models/gcn.py:16-30;
+ * 1.5D: 1D_CAGNET/dist_15d.py:61-106).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer on the current CUDA device unless the name says host_;
+ *   - dense matrices are row-major fp32, sparse indices int32 (base 0), row offsets int64;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream); all work is
+ *     enqueued asynchronously unless stated otherwise;
+ *   - every function returns 0 on success, a negative DG_ERR_* for rejected arguments, a positive
+ *     cudaError_t for CUDA failures and 10000 + ncclResult_t for NCCL failures; nothing throws.
+ */
+#ifndef DIST_GNN_B200_H
+#define DIST_GNN_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DG_OK                 0
+#define DG_ERR_NULL          -1   /* a required pointer is NULL */
+#define DG_ERR_DIMS          -2   /* negative or inconsistent sizes / leading dimensions */
+#define DG_ERR_INDEX         -3   /* row ids not ascending, or an index outside [0,m) x [0,k) */
+#define DG_ERR_UNSUPPORTED   -4   /* valid request this build does not implement */
+#define DG_ERR_STATE         -5   /* object used in the wrong state (e.g. destroyed, wrong device) */
+#define DG_ERR_SCRATCH       -6   /* request needs more scratch than the fixed-size variant holds */
+#define DG_NCCL_ERROR_BASE    10000
+
+/* epilogue_flags of dg_spmm_csr: out[i,:] = act( row_scale[i] * (alpha*A*B + beta*C)[i,:] + bias ) */
+#define DG_EPI_ROW_SCALE      1u  /* multiply row i by row_scale[i]  (e.g. a D^-1/2 factor kept out of A's values) */
+#define DG_EPI_BIAS           2u  /* add bias[f] to column f */
+#define DG_EPI_RELU           4u  /* max(x, 0) last */
+
+typedef struct dg_plan dg_plan;   /* CSR view + degree bins of one sparse block, lives on one device */
+typedef struct dg_comm dg_comm;   /* one NCCL communicator with its side stream and events */
+
+typedef struct dg_plan_stats {
+    int64_t nnz;
+    int32_t m, k;
+    int32_t heavy_threshold;      /* rows with more entries than this are split into chunks */
+    int32_t chunk;                /* entries per chunk of a split row */
+    int32_t heavy_rows;           /* number of split rows */
+    int32_t heavy_chunks;         /* total chunks (scratch rows) */
+    int64_t heavy_nnz;            /* entries inside split rows */
+    int64_t max_row_nnz;
+    int64_t touched_columns;      /* distinct column ids in the block (for compulsory-traffic accounting) */
+} dg_plan_stats;
+
+const char* dg_strerror(int code);
+int dg_version(void);
+
+/* ---- plan: COO (row-sorted, as torch's coalesce() leaves it) -> CSR row offsets + degree bins -----------------
+ * Replaces the per-call descriptor set-up of spmm.cpp:19-24 (and the coo2csr of spmm_original.cpp:140-146) by a
+ * one-off step.  `row` is only read during creation; `col` is BORROWED: it must stay valid and unchanged for the
+ * life of the plan.  Validates ordering and ranges on the device and returns DG_ERR_INDEX instead of launching
+ * anything on bad input.  Synchronises `stream` once (one-off cost).  heavy_threshold/chunk <= 0 pick defaults. */
+int dg_plan_create(const int32_t* row, const int32_t* col, int64_t nnz, int32_t m, int32_t k,
+                   void* stream, dg_plan** out);
+int dg_plan_create_ex(const int32_t* row, const int32_t* col, int64_t nnz, int32_t m, int32_t k,
+                      int32_t heavy_threshold, int32_t chunk, void* stream, dg_plan** out);
+int dg_plan_destroy(dg_plan* plan);
+int dg_plan_get_stats(const dg_plan* plan, dg_plan_stats* host_out);
+/* copies the m+1 row offsets to host memory (synchronises `stream`); used to check CSR indexing bit for bit */
+int dg_plan_copy_rowptr(const dg_plan* plan, int64_t* host_rowptr, void* stream);
+
+/* ---- local product: C = epilogue(alpha * A * B + beta * C) ------------------------------------------------------
+ * A = plan (m x k) with values `val` (nnz, in the COO order the plan was built from); B is k x F with leading
+ * dimension ldb, C is m x F with leading dimension ldc (in floats).  beta == 0 never reads C.  Replaces
+ * cusparseSpMM(COO_ALG4) at spmm.cpp:26-28.  Results are bit-reproducible run to run (no float atomics).
+ * Split rows use plan-owned scratch that grows on first use for a wider F (that call allocates and
+ * synchronises); two products on the same plan must not overlap in time. */
+int dg_spmm_csr(const dg_plan* plan, const float* val, const float* B, int64_t ldb, float* C, int64_t ldc,
+                int32_t F, float alpha, float beta, uint32_t epilogue_flags, const float* row_scale,
+                const float* bias, void* stream);
+
+/* ---- drop-in for spmm_cusparse(row, col, val, A_row, A_col, B, C, alpha, beta) (spmm.cpp:17) ----------------------
+ * Same nine operands plus the dense width F and the stream; B is k x F and C is m x F, both contiguous.
+ * Builds a transient plan per call (allocates and synchronises); callers that reuse a block should hold a plan. */
+int dg_spmm_coo(const int32_t* row, const int32_t* col, const float* val, int64_t nnz, int32_t m, int32_t k,
+                const float* B, float* C, int32_t F, float alpha, float beta, void* stream);
+
+/* ---- communicators (NCCL over NVLink / NVSwitch) ------------------------------------------------------------------
+ * Replace the torch.distributed process groups the stage loop broadcasts in (light_dist_gnn/dist_utils/env.py:47-54;
+ * 1.5D row / column groups: 1D_CAGNET/utils.py:36-49).  One process per GPU; rank 0 makes an id, every rank passes
+ * the same 128 bytes to dg_comm_create with the device it will use current.  dg_comm_split makes the sub-groups. */
+int dg_comm_unique_id(char host_id_out[128]);
+int dg_comm_create(const char host_id[128], int rank, int nranks, dg_comm** out);
+int dg_comm_split(dg_comm* parent, int color, int key, dg_comm** out);
+int dg_comm_destroy(dg_comm* comm);
+int dg_comm_rank(const dg_comm* comm, int* rank, int* nranks);
+/* in-place sum over the communicator, enqueued on `stream` (dW of gcn.py:52; the partial z of dist_15d.py:104) */
+int dg_comm_allreduce_sum(dg_comm* comm, float* buf, int64_t count, void* stream);
+int dg_comm_broadcast(dg_comm* comm, float* buf, int64_t count, int root, void* stream);
+
+typedef struct dg_stage_times {   /* device times of the last timed stage loop on a communicator, milliseconds */
+    float comm_ms;                /* sum over stages of broadcast durations on the side stream */
+    float spmm_ms;                /* sum over stages of local-product durations on the compute stream */
+    float total_ms;               /* first enqueue to last completion */
+    int32_t stages;
+} dg_stage_times;
+
+/* ---- the stage loop: z = sum_s A[.,part_s] * X_{root_s} --------------------------------------------------------------
+ * Replaces models/gcn.py:16-30.  For stage s the block of rank roots[s] (of `comm`) is broadcast on the
+ * communicator's side stream into recv[s % nbuf] (the root sends `x_local` in place) while the compute stream
+ * multiplies the block of stage s-1; events chain the two streams, nothing blocks the host.
+ *   plans[s], vals[s]   plan and values of the sparse block multiplied at stage s (n x n)
+ *   x_local             this rank's n x F block (read when this rank is a root, and never copied)
+ *   recv[0..nbuf)       nbuf >= 2 device buffers of n*F floats owned by the caller
+ *   z                   n x F result on the compute stream; overwritten (the first stage runs with beta = 0)
+ *   timed != 0          record per-stage events; read them with dg_comm_last_times after synchronising
+ * With a NULL comm or a single rank the loop degenerates to local products and no collective.  The summation order
+ * is the reference's: stages in the order given, ascending column inside a row. */
+int dg_bcast_spmm_1d(dg_comm* comm, int32_t n_stages, const int32_t* host_roots,
+                     const dg_plan* const* host_plans, const float* const* host_vals,
+                     const float* x_local, int32_t n, int32_t F, float* const* host_recv, int32_t nbuf,
+                     float* z, int timed, void* compute_stream);
+/* 1.5D (dist_15d.py:61-106): the same loop inside the column communicator, then the sum of the partial z over
+ * the row communicator (replication group). */
+int dg_bcast_spmm_15d(dg_comm* col_comm, dg_comm* row_comm, int32_t n_stages, const int32_t* host_roots,
+                      const dg_plan* const* host_plans, const float* const* host_vals,
+                      const float* x_local, int32_t n, int32_t F, float* const* host_recv, int32_t nbuf,
+                      float* z, int timed, void* compute_stream);
+int dg_comm_last_times(dg_comm* comm, dg_stage_times* host_out);
+
+/* ---- instrumentation (no counterpart in the reference, whose timer synchronises the device around every call,
+ * light_dist_gnn/dist_utils/timer.py:16-24) ------------------------------------------------------------------------
+ * Between dg_profile_begin and dg_profile_end every local product is bracketed by a CUDA event pair on the stream it
+ * is launched on.  dg_profile_end synchronises the device and reports the summed device time of the products, their
+ * algorithmic traffic  8*nnz + 4*(m+1) + 4*F*touched_columns + 4*F*m*(1 + [beta != 0])  in bytes, the no-reuse gather
+ * volume  8*nnz + 4*(m+1) + 4*F*nnz + 4*F*m*(1 + [beta != 0]),  2*nnz*F flops, and how many kernels of this library
+ * were launched (products only; NCCL's own kernels are not counted). */
+typedef struct dg_profile {
+    double spmm_ms;
+    double alg_bytes;
+    double gather_bytes;
+    double flops;
+    int64_t products;
+    int64_t kernel_launches;
+} dg_profile;
+int dg_profile_begin(void);
+int dg_profile_end(dg_profile* host_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DIST_GNN_B200_H */

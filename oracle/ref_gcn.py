@@ -231,3 +231,61 @@ def gcn_15d(parted_blocks, weights, P, c):
         blocks = [per_rank[b * c] for b in range(P // c)]      # replicas of a row group hold equal blocks
         return broadcast_15d(adj, blocks, P, c)
     return GcnOracle(bcast, weights, cols)
+
+
+# ---------------------------------------------------------------- timed CPU baseline (torch sparse path)
+def cpu_epoch_sample(adj_block, x_full, labels, train_mask, weights, threads, stand_in_seed=0):
+    """One GCN epoch of ONE rank's share, on the CPU, with the calls the reference makes on its CPU/gloo path:
+    z.addmm_(A, B) for the sparse product (light_dist_gnn/models/gcn.py:13), torch.mm for the dense ones
+    (gcn.py:41, :49-50), CrossEntropyLoss over the local train rows and Adam (dist_train.py:30-45).
+
+    adj_block   torch sparse COO [n x N], the rank's row block of the normalised adjacency (all column blocks joined:
+                the reference multiplies them one broadcast stage at a time, the work is the same)
+    x_full      [N x d0] features of every rank (what the stage-loop broadcasts deliver for layer 1)
+    For the deeper layers and for backward, the blocks other ranks would broadcast are stood in for by a fixed
+    random [N x width] matrix whose rows [0, n) are overwritten with this rank's own activations / gradients; the
+    arithmetic volume is exactly that of a rank in a 1D partition, with no communication time.
+    Returns (seconds, loss)."""
+    import time
+    import torch
+    torch.set_num_threads(threads)
+    n, N = adj_block.shape
+    gen = torch.Generator().manual_seed(stand_in_seed)
+    widths = sorted({w.shape[1] for w in weights})
+    stand_in = {w: torch.randn(N, w, generator=gen) * 0.01 for w in widths}
+    ws = [w.clone() for w in weights]
+    L = len(ws)
+    t0 = time.perf_counter()
+    # forward
+    xs, zs, ys = [], [], []
+    b_full = x_full
+    for l, w in enumerate(ws):
+        z = torch.zeros(n, b_full.shape[1])
+        z.addmm_(adj_block, b_full)
+        y = torch.mm(z, w)
+        xs.append(b_full[:n])
+        zs.append(z)
+        ys.append(y)
+        if l < L - 1:
+            b_full = stand_in[y.shape[1]]
+            b_full[:n] = torch.relu(y)
+    out = ys[-1].requires_grad_(True)
+    idx = train_mask.nonzero().squeeze(1)
+    loss = torch.nn.functional.cross_entropy(out[idx], labels[idx]) if idx.numel() else (out * 0).sum()
+    g = torch.autograd.grad(loss, out)[0]
+    # backward
+    grads = [None] * L
+    for l in range(L - 1, -1, -1):
+        if l < L - 1:
+            g = g * (ys[l] > 0)
+        g_full = stand_in[g.shape[1]]
+        g_full[:n] = g
+        ag = torch.zeros(n, g.shape[1])
+        ag.addmm_(adj_block, g_full)
+        grads[l] = torch.mm(xs[l].t(), ag)
+        g = torch.mm(ag, ws[l].t())
+    # Adam, first step (m = (1-b1) g, v = (1-b2) g^2)
+    for l in range(L):
+        m, v = 0.1 * grads[l], 0.001 * grads[l] * grads[l]
+        ws[l] = ws[l] - 0.01 * (m / 0.1) / ((v / 0.001).sqrt() + 1e-8)
+    return time.perf_counter() - t0, float(loss.detach())
