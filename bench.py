@@ -40,6 +40,8 @@ def parse():
     ap.add_argument('--layers', type=int, default=0, help='override the number of GCN layers')
     ap.add_argument('--seed', type=int, default=0)
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--profiler-range', action='store_true',
+                    help='cudaProfilerStart/Stop around the device-resident timed steps (for ncu --profile-from-start off)')
     ap.add_argument('--no-permute', action='store_true', help='keep the raw R-MAT vertex order (skewed row blocks)')
     return ap.parse_args()
 
@@ -174,11 +176,15 @@ def run_ours(args):
     fence()
     with ClockSampler(env.device.index) as clocks:
         spmm_cpp.profile_begin()
+        if args.profiler_range:
+            torch.cuda.profiler.start()
         ev0.record()
         for _ in range(args.steps):
             loss = epoch_step()
         ev1.record()
         fence()
+        if args.profiler_range:
+            torch.cuda.profiler.stop()
         prof = spmm_cpp.profile_end()
     ms_total = max_over_ranks(ev0.elapsed_time(ev1))
     final_loss = float(loss.item())

@@ -156,7 +156,7 @@ def test_full_size_graph_and_spmm_properties(big_graph):
         cols = idx[1, e0:e1]
         sub = ref_graph.Coo(np.zeros(e1 - e0, np.int64), np.arange(e1 - e0, dtype=np.int64), val[e0:e1].cpu().numpy(), (1, e1 - e0))
         want = ref_gcn.spmm_coo(sub, np.ascontiguousarray(X[cols].cpu().numpy()), np.zeros((1, F), np.float32), 1.0, 0.0)
-        assert np.abs(AX[i].cpu().numpy() - want[0]).max() <= 1e-5 * max(np.abs(want).max(), 1e-3), i
+        assert np.abs(AX[i].cpu().numpy() - want[0]).max() <= 1e-5 * scale, i      # per-tensor scale, as everywhere
 
     # the stage structure: 4 column blocks accumulated in order == one block
     from coo_graph import graph_utils
