@@ -1,0 +1,47 @@
+"""The C-ABI shared library loads without a GPU and exports every function include/dist_gnn_b200.h declares."""
+import ctypes
+import os
+import re
+
+from conftest import PKG, ROOT
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, 'include', 'dist_gnn_b200.h')).read()
+    text = re.sub(r'/\*.*?\*/', '', text, flags=re.S)
+    return sorted(set(re.findall(r'\b(dg_[a-z0-9_]+)\s*\(', text)))
+
+
+def test_library_loads_and_exports_every_declared_symbol():
+    path = os.path.join(PKG, 'csrc', 'libdist_gnn_b200.so')
+    assert os.path.exists(path), 'build the library first: python dist-gnn_b200/csrc/build.py'
+    import torch  # noqa: F401  (loads the NCCL the library links against)
+    lib = ctypes.CDLL(path)
+    names = declared_functions()
+    assert len(names) >= 20
+    for name in names:
+        assert hasattr(lib, name), f'{name} is declared in the header but not exported'
+    lib.dg_strerror.restype = ctypes.c_char_p
+    assert lib.dg_version() >= 100
+    assert lib.dg_strerror(0) == b'ok' and b'row-sorted' in lib.dg_strerror(-3)
+
+
+def test_argument_checks_need_no_gpu():
+    import spmm_cpp
+    L = spmm_cpp.lib()
+    out = ctypes.c_void_p()
+    assert L.dg_plan_create(None, None, -1, 1, 1, None, ctypes.byref(out)) == -2      # negative nnz
+    assert L.dg_plan_create(None, None, 5, 1, 1, None, ctypes.byref(out)) == -1       # entries but no arrays
+    assert L.dg_plan_create(None, None, 0, 1, 1, None, None) == -1                    # no output slot
+    assert L.dg_spmm_csr(None, None, None, 1, None, 1, 1, 1.0, 0.0, 0, None, None, None) == -1
+    assert L.dg_comm_create(None, 0, 1, ctypes.byref(out)) == -1
+    assert L.dg_plan_destroy(None) == 0 and L.dg_comm_destroy(None) == 0
+
+
+def test_product_modules_do_not_import_the_oracle():
+    for folder, _, files in os.walk(PKG):
+        for f in files:
+            if f.endswith('.py') or f.endswith('.cu') or f.endswith('.h'):
+                text = open(os.path.join(folder, f)).read()
+                assert not re.search(r'^\s*(from|import)\s+oracle\b|oracle[/.](ref_|spmm_ref|_build|_ref)', text, flags=re.M), \
+                    f'{f} reaches into the oracle'

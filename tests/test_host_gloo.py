@@ -1,0 +1,141 @@
+"""Host-side logic of the N>1 path on CPU ranks over gloo: DistEnv groups, the stage schedules, the partition files
+and loaders.  The sparse product inside the loop is done by the oracle here, from the test only - the product has no
+CPU engine, which one of the tests checks."""
+import os
+import sys
+import tempfile
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN, PKG, ROOT, assert_close
+
+
+def _dataset(z):
+    n, e, c = (int(v) for v in z['in/meta'])
+    m = torch.from_numpy(z['in/masks'])
+    return dict(edge_index=torch.from_numpy(z['in/edge_index']), features=torch.from_numpy(z['in/features']),
+                labels=torch.from_numpy(z['in/labels']), train_mask=m[0], val_mask=m[1], test_mask=m[2],
+                num_nodes=n, num_edges=e, num_classes=c)
+
+
+def _worker(rank, world, rep, port, data_root, out_dir):
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port), DIST_GNN_DATA_ROOT=data_root, DIST_GNN_LOG_ROOT=out_dir)
+    for p in (ROOT, PKG):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import torch.distributed as dist
+    from coo_graph import Parted_COO_Graph
+    from dist_utils import DistEnv
+    from models.gcn import broadcast
+    from oracle import ref_gcn, ref_graph
+    torch.set_num_threads(1)
+    env = DistEnv(rank, world, 'gloo', rep=rep)
+    try:
+        assert env.device.type == 'cpu' and env.comm is None
+        g = Parted_COO_Graph('gsmall', rank // rep, world // rep, device=env.device)
+        rec = {}
+        try:
+            broadcast(g.adj_parts, g.features, 'x')
+            rec['cpu_refused'] = False
+        except RuntimeError as e:
+            rec['cpu_refused'] = 'no CPU path' in str(e)
+        # the stage loop, executed by the test: gloo broadcasts in the schedule's group + oracle products
+        group = env.col_groups[env.rank_col] if rep > 1 else env.world_group
+        x = g.features.clone()
+        z = np.zeros(tuple(x.shape), dtype=np.float32)
+        for st in env.stages():
+            buf = x.clone() if st.root_global == rank else torch.zeros_like(x)
+            dist.broadcast(buf, src=st.root_global, group=group)
+            a = g.adj_parts[st.part]
+            idx = a.indices().numpy()
+            ref_gcn.spmm_coo(ref_graph.Coo(idx[0], idx[1], a.values().numpy(), tuple(a.shape)), buf.numpy(), z, 1.0, 1.0)
+        zt = torch.from_numpy(z)
+        if rep > 1:
+            dist.all_reduce(zt, group=env.row_groups[env.rank_grp])
+        rec['z'] = zt.numpy()
+        w = torch.full((3, 2), float(rank + 1))
+        env.all_reduce_sum(w)                                   # dW reduction group: world (1D) or column group (1.5D)
+        rec['w'] = w.numpy()
+        rec['gathered'] = env.all_gather_then_cat(torch.full((2, 1), float(rank // rep))).numpy()
+        with env.timer.timing('epoch'):
+            pass
+        summary = env.timer.summary_all()
+        rec['summary_ok'] = 'epoch' in summary
+        env.logger.log('hello from', rank)
+        rec['log_ok'] = os.path.exists(os.path.join(out_dir, f'logs_{world}', f'all_log_{rank}.txt'))
+        np.savez(os.path.join(out_dir, f'rank{rank}.npz'), **rec)
+    finally:
+        env.shutdown()
+
+
+def _run(world, rep, port):
+    import torch.multiprocessing as mp
+    from coo_graph import COO_Graph, datasets
+    z = np.load(os.path.join(GOLDEN, 'graph_small.npz'))
+    data_root, out_dir = tempfile.mkdtemp(prefix='dg_gloo_data_'), tempfile.mkdtemp(prefix='dg_gloo_out_')
+    old = datasets.data_root
+    datasets.data_root = data_root
+    try:
+        datasets.save_dataset(name='gsmall', **_dataset(z))
+        COO_Graph('gsmall').partition(world // rep)
+    finally:
+        datasets.data_root = old
+    mp.spawn(_worker, (world, rep, port, data_root, out_dir), nprocs=world, join=True)
+    return z, [np.load(os.path.join(out_dir, f'rank{r}.npz')) for r in range(world)]
+
+
+def _oracle_parts(z, R):
+    from oracle import ref_graph
+    n = int(z['in/meta'][0])
+    A = ref_graph.Coo(z['full/adj_idx'][0], z['full/adj_idx'][1], z['full/adj_val'], (n, n))
+    return [ref_graph.parted_graph(p) for p in ref_graph.partition(A, z['full/features'], z['in/labels'].astype(np.int64), z['in/masks'], R)]
+
+
+def test_1d_schedule_over_two_gloo_ranks_matches_reference(golden):
+    z, res = _run(2, 1, 29811)
+    t = golden('gcn_small')
+    for r in range(2):
+        assert bool(res[r]['cpu_refused'])
+        assert_close(res[r]['z'], t[f'r{r}/bcast_0'], 1e-5, f'rank {r} vs the reference over gloo')
+        assert np.array_equal(res[r]['w'], np.full((3, 2), 3.0))
+        assert np.array_equal(res[r]['gathered'].ravel(), [0, 0, 1, 1])
+        assert bool(res[r]['summary_ok']) and bool(res[r]['log_ok'])
+
+
+def test_15d_schedule_over_four_gloo_ranks_matches_oracle_and_1d(golden):
+    from oracle import ref_gcn
+    z, res = _run(4, 2, 29813)
+    parts = _oracle_parts(z, 2)
+    want = ref_gcn.broadcast_15d([p['adj_parts'] for p in parts], [p['features'] for p in parts], 4, 2)
+    one_d = ref_gcn.broadcast_1d([p['adj_parts'] for p in parts], [p['features'] for p in parts])
+    for r in range(4):
+        assert_close(res[r]['z'], want[r], 1e-5, f'rank {r} vs 1.5D oracle')
+        assert_close(res[r]['z'], one_d[r // 2], 1e-5, f'rank {r} vs 1D over the same 2 row blocks')
+        # dW is summed over the column group {r%2, r%2+2}: ranks (1,3) -> 1+3... with values rank+1
+        assert np.array_equal(res[r]['w'], np.full((3, 2), float((r % 2 + 1) + (r % 2 + 3))))
+        assert np.array_equal(res[r]['gathered'].ravel(), [0, 0, 1, 1])
+
+
+def test_schedule_shapes():
+    from dist_utils import schedule
+    assert [tuple(s) for s in schedule.stages_1d(3)] == [(0, 0, 0), (1, 1, 1), (2, 2, 2)]
+    # 8 ranks, c = 2: 4 row blocks, 2 stages each; replica 0 takes column blocks 0,1 and replica 1 takes 2,3
+    assert [s.part for s in schedule.stages_15d(0, 8, 2)] == [0, 1] and [s.root_global for s in schedule.stages_15d(0, 8, 2)] == [0, 2]
+    assert [s.part for s in schedule.stages_15d(7, 8, 2)] == [2, 3] and [s.root_global for s in schedule.stages_15d(7, 8, 2)] == [5, 7]
+    assert schedule.row_groups(8, 2) == [[0, 1], [2, 3], [4, 5], [6, 7]]
+    assert schedule.col_groups(8, 2) == [[0, 2, 4, 6], [1, 3, 5, 7]]
+    # the last replica takes the remainder: 12 ranks, c = 3 -> 4 row blocks, P // c^2 = 1 stage each, last replica 2 stages
+    assert [len(schedule.stages_15d(r, 12, 3)) for r in range(3)] == [1, 1, 2]
+    covered = sorted(s.part for r in range(3) for s in schedule.stages_15d(r, 12, 3))
+    assert covered == [0, 1, 2, 3]
+    for P, c in ((4, 2), (8, 2), (9, 3), (12, 3), (16, 4)):
+        for rank in range(P):
+            for s in schedule.stages_15d(rank, P, c):
+                assert s.root_global % c == rank % c and s.root_global // c == s.part
+                assert schedule.col_groups(P, c)[rank % c][s.root_in_group] == s.root_global
+    with pytest.raises(ValueError):
+        schedule.check_layout(6, 4)
+    with pytest.raises(ValueError):
+        schedule.check_layout(2, 2)
