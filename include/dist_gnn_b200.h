@@ -80,6 +80,18 @@ int dg_spmm_csr(const dg_plan* plan, const float* val, const float* B, int64_t l
                 int32_t F, float alpha, float beta, uint32_t epilogue_flags, const float* row_scale,
                 const float* bias, void* stream);
 
+/* ---- the same product without any device allocation (no counterpart in the reference) --------------------------------
+ * For hosts that cannot let a library call cudaMalloc: all device memory already sits in their own pool, or they run
+ * a latency-critical loop that must not take the device-wide synchronisation an allocation implies.  Identical
+ * arguments and results to dg_spmm_csr, but the partial sums of split rows go to a fixed 16 MiB array inside the
+ * library image (held by every GPU that loads the library, shared by all calls on that GPU).  Returns DG_ERR_SCRATCH
+ * when heavy_chunks * F exceeds dg_static_scratch_capacity() floats.  Calls that overlap in time on one GPU race on
+ * the array; the first call on a device resolves the array's address and should happen before any stream capture. */
+int dg_spmm_csr_static(const dg_plan* plan, const float* val, const float* B, int64_t ldb, float* C, int64_t ldc,
+                       int32_t F, float alpha, float beta, uint32_t epilogue_flags, const float* row_scale,
+                       const float* bias, void* stream);
+int64_t dg_static_scratch_capacity(void);
+
 /* ---- drop-in for spmm_cusparse(row, col, val, A_row, A_col, B, C, alpha, beta) (spmm.cpp:17) ----------------------
  * Same nine operands plus the dense width F and the stream; B is k x F and C is m x F, both contiguous.
  * Builds a transient plan per call (allocates and synchronises); callers that reuse a block should hold a plan. */
