@@ -27,6 +27,17 @@ struct dg_heavy_row {
     int32_t pad;
 };
 
+// One row whose entries span more than one task of the streaming kernel: its partial sums sit in carry slots
+// 2*t_first+1 (the piece that starts the row) and 2*t (t_first < t <= t_last, pieces that continue it).
+struct dg_split_row {
+    int32_t row;
+    int32_t t_first;
+    int32_t t_last;
+    int32_t pad;
+};
+
+#define DG_DEFAULT_TASK_NNZ 1024
+
 struct dg_plan {
     int device;
     int32_t m, k;
@@ -38,14 +49,33 @@ struct dg_plan {
     dg_heavy_row* heavy;      // device, n_heavy
     int32_t n_chunks, n_heavy;
     int64_t heavy_nnz, max_row_nnz, touched_columns;
-    float* scratch;           // device, n_chunks x scratch_ld floats, grown on demand
+    float* scratch;           // device, grown on demand to dg_scratch_floats(plan, F)
     int64_t scratch_floats;
+    // streaming kernel: the entry list cut into tasks of task_nnz entries, one warp each
+    int32_t task_nnz, n_tasks, n_split;
+    int32_t* task_first_row;  // device, n_tasks: the row that holds entry t * task_nnz
+    dg_split_row* split;      // device, n_split rows that span tasks, ascending
+    int* status;              // device word: set non-zero by a kernel that gave up on a bounded wait
 };
+
+// Scratch floats one product of width F may touch: split-row chunks (row kernels) or two carry rows per task (streaming).
+static inline int64_t dg_scratch_floats(const dg_plan* p, int32_t F)
+{
+    const int64_t a = (int64_t)p->n_chunks * F, b = 2 * (int64_t)p->n_tasks * F;
+    return a > b ? a : b;
+}
+int dg_spmm_stream_eligible(const dg_plan* plan, const float* B, int64_t ldb, const float* C, int64_t ldc, int32_t F);
+int dg_spmm_stream_launch(const dg_plan* plan, const float* val, const float* B, int64_t ldb, float* C, int64_t ldc,
+                          int32_t F, float alpha, float beta, uint32_t flags, const float* row_scale, const float* bias,
+                          float* scratch, cudaStream_t stream, int* launches);
 
 // Launches the product with an explicit scratch area (n_chunks x F floats); shared by the plan-owned and the
 // fixed-scratch entry points.
 int dg_spmm_launch(const dg_plan* plan, const float* val, const float* B, int64_t ldb, float* C, int64_t ldc,
                    int32_t F, float alpha, float beta, uint32_t flags, const float* row_scale, const float* bias,
                    float* scratch, cudaStream_t stream);
+int dg_spmm_launch_rows(const dg_plan* plan, const float* val, const float* B, int64_t ldb, float* C, int64_t ldc,
+                        int32_t F, float alpha, float beta, uint32_t flags, const float* row_scale, const float* bias,
+                        float* scratch, cudaStream_t stream);
 int dg_check_spmm_args(const dg_plan* plan, const float* val, const float* B, int64_t ldb, const float* C, int64_t ldc,
                        int32_t F, uint32_t flags, const float* row_scale, const float* bias);

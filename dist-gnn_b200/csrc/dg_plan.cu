@@ -76,6 +76,35 @@ __global__ void k_count_bits(const uint32_t* __restrict__ bitmap, int64_t words,
     if ((threadIdx.x & 31) == 0 && local) atomicAdd(total, local);
 }
 
+// Thread t: the row that holds entry t * task_nnz, i.e. the smallest r with rowptr[r + 1] > t * task_nnz.
+__global__ void k_task_first_row(const int64_t* __restrict__ rowptr, int32_t m, int64_t task_nnz, int32_t n_tasks,
+                                 int32_t* __restrict__ first_row)
+{
+    const int32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n_tasks) return;
+    const int64_t e = (int64_t)t * task_nnz;
+    int32_t lo = 0, hi = m;            // answer in [0, m): entry e exists, so some row ends beyond it
+    while (lo < hi) {
+        const int32_t mid = lo + (hi - lo) / 2;
+        if (rowptr[mid + 1] > e) hi = mid; else lo = mid + 1;
+    }
+    first_row[t] = lo;
+}
+
+// Rows whose entries fall into more than one task.
+__global__ void k_split_census(const int64_t* __restrict__ rowptr, int32_t m, int64_t task_nnz,
+                               dg_split_row* __restrict__ out, int32_t capacity, int32_t* __restrict__ count)
+{
+    const int32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= m) return;
+    const int64_t e0 = rowptr[i], e1 = rowptr[i + 1];
+    if (e1 <= e0) return;
+    const int64_t t0 = e0 / task_nnz, t1 = (e1 - 1) / task_nnz;
+    if (t0 == t1) return;
+    const int32_t slot = atomicAdd(count, 1);
+    if (slot < capacity) out[slot] = dg_split_row{i, (int32_t)t0, (int32_t)t1, 0};
+}
+
 struct DeviceTemp {   // frees its allocations on scope exit
     std::vector<void*> ptrs;
     ~DeviceTemp() { for (void* p : ptrs) cudaFree(p); }
@@ -86,7 +115,62 @@ struct DeviceTemp {   // frees its allocations on scope exit
     }
 };
 
+int build_tasks(dg_plan* p, int32_t task_nnz, cudaStream_t stream)
+{
+    cudaFree(p->task_first_row);
+    cudaFree(p->split);
+    p->task_first_row = nullptr;
+    p->split = nullptr;
+    p->task_nnz = task_nnz;
+    p->n_tasks = (int32_t)((p->nnz + task_nnz - 1) / task_nnz);
+    p->n_split = 0;
+    if (p->n_tasks == 0) return DG_OK;
+    const int T = 256;
+    DG_CUDA(cudaMalloc((void**)&p->task_first_row, (size_t)p->n_tasks * sizeof(int32_t)));
+    k_task_first_row<<<(p->n_tasks + T - 1) / T, T, 0, stream>>>(p->rowptr, p->m, task_nnz, p->n_tasks, p->task_first_row);
+    DeviceTemp tmp;
+    dg_split_row* d_rows = nullptr;
+    int32_t* d_count = nullptr;
+    const int32_t capacity = p->n_tasks;      // a row can only be cut at one of the n_tasks - 1 task boundaries
+    DG_CUDA(tmp.alloc(&d_rows, (size_t)capacity));
+    DG_CUDA(tmp.alloc(&d_count, 1));
+    DG_CUDA(cudaMemsetAsync(d_count, 0, sizeof(int32_t), stream));
+    k_split_census<<<(p->m + T - 1) / T, T, 0, stream>>>(p->rowptr, p->m, task_nnz, d_rows, capacity, d_count);
+    int32_t h_count = 0;
+    DG_CUDA(cudaMemcpyAsync(&h_count, d_count, sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+    DG_CUDA(cudaStreamSynchronize(stream));
+    DG_CUDA(cudaGetLastError());
+    if (h_count > capacity) return DG_ERR_STATE;
+    if (h_count > 0) {
+        std::vector<dg_split_row> rows((size_t)h_count);
+        DG_CUDA(cudaMemcpy(rows.data(), d_rows, rows.size() * sizeof(dg_split_row), cudaMemcpyDeviceToHost));
+        std::sort(rows.begin(), rows.end(), [](const dg_split_row& a, const dg_split_row& b) { return a.row < b.row; });
+        DG_CUDA(cudaMalloc((void**)&p->split, rows.size() * sizeof(dg_split_row)));
+        DG_CUDA(cudaMemcpy(p->split, rows.data(), rows.size() * sizeof(dg_split_row), cudaMemcpyHostToDevice));
+        p->n_split = h_count;
+    }
+    return DG_OK;
+}
+
 }  // namespace
+
+extern "C" int dg_plan_set_task_size(dg_plan* p, int32_t task_nnz, void* stream)
+{
+    if (!p) return DG_ERR_NULL;
+    if (task_nnz <= 0) task_nnz = DG_DEFAULT_TASK_NNZ;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev != p->device) return DG_ERR_STATE;
+    DG_CUDA(cudaStreamSynchronize((cudaStream_t)stream));     // earlier products may still read the old tables
+    return build_tasks(p, task_nnz, (cudaStream_t)stream);
+}
+
+extern "C" int dg_plan_device_status(const dg_plan* p, int* host_status, void* stream)
+{
+    if (!p || !host_status) return DG_ERR_NULL;
+    DG_CUDA(cudaMemcpyAsync(host_status, p->status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    DG_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return DG_OK;
+}
 
 extern "C" int dg_plan_create_ex(const int32_t* row, const int32_t* col, int64_t nnz, int32_t m, int32_t k,
                                  int32_t heavy_threshold, int32_t chunk, void* stream_, dg_plan** out)
@@ -173,6 +257,8 @@ extern "C" int dg_plan_create_ex(const int32_t* row, const int32_t* col, int64_t
             (rc = (int)cudaMemcpy(p->heavy, heavy.data(), heavy.size() * sizeof(dg_heavy_row), cudaMemcpyHostToDevice)))
             return fail(rc);
     }
+    if ((rc = (int)cudaMalloc((void**)&p->status, sizeof(int))) || (rc = (int)cudaMemset(p->status, 0, sizeof(int)))) return fail(rc);
+    if ((rc = build_tasks(p, DG_DEFAULT_TASK_NNZ, stream))) return fail(rc);
     *out = p;
     return DG_OK;
 }
@@ -193,6 +279,9 @@ extern "C" int dg_plan_destroy(dg_plan* p)
     cudaFree(p->chunks);
     cudaFree(p->heavy);
     cudaFree(p->scratch);
+    cudaFree(p->task_first_row);
+    cudaFree(p->split);
+    cudaFree(p->status);
     if (prev != p->device && prev >= 0) cudaSetDevice(prev);
     delete p;
     return DG_OK;

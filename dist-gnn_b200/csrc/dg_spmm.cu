@@ -309,9 +309,9 @@ int dg_check_spmm_args(const dg_plan* plan, const float* val, const float* B, in
     return DG_OK;
 }
 
-int dg_spmm_launch(const dg_plan* plan, const float* val, const float* B, int64_t ldb, float* C, int64_t ldc,
-                   int32_t F, float alpha, float beta, uint32_t flags, const float* row_scale, const float* bias,
-                   float* scratch, cudaStream_t stream)
+int dg_spmm_launch_rows(const dg_plan* plan, const float* val, const float* B, int64_t ldb, float* C, int64_t ldc,
+                        int32_t F, float alpha, float beta, uint32_t flags, const float* row_scale, const float* bias,
+                        float* scratch, cudaStream_t stream)
 {
     if (plan->m == 0 || F == 0) return DG_OK;
     SpmmArgs a{};
@@ -326,6 +326,20 @@ int dg_spmm_launch(const dg_plan* plan, const float* val, const float* B, int64_
     if (F % 4 == 0 && ldb % 4 == 0 && ldc % 4 == 0 && aligned(B, 16) && aligned(C, 16)) vec = 4;
     else if (F % 2 == 0 && ldb % 2 == 0 && ldc % 2 == 0 && aligned(B, 8) && aligned(C, 8)) vec = 2;
     a.nvec = F / vec;
+    switch (vec) {
+        case 4: return launch_vec<4>(a, stream);
+        case 2: return launch_vec<2>(a, stream);
+        default: return launch_vec<1>(a, stream);
+    }
+}
+
+// Picks the kernel family (streaming when the operands allow it, row kernels otherwise) and brackets the product with
+// profile events while a profile is open.
+int dg_spmm_launch(const dg_plan* plan, const float* val, const float* B, int64_t ldb, float* C, int64_t ldc,
+                   int32_t F, float alpha, float beta, uint32_t flags, const float* row_scale, const float* bias,
+                   float* scratch, cudaStream_t stream)
+{
+    if (plan->m == 0 || F == 0) return DG_OK;
     bool profiled = false;
     {
         std::lock_guard<std::mutex> lock(g_profile.mu);
@@ -339,10 +353,12 @@ int dg_spmm_launch(const dg_plan* plan, const float* val, const float* B, int64_
         }
     }
     int rc;
-    switch (vec) {
-        case 4: rc = launch_vec<4>(a, stream); break;
-        case 2: rc = launch_vec<2>(a, stream); break;
-        default: rc = launch_vec<1>(a, stream); break;
+    if (dg_spmm_stream_eligible(plan, B, ldb, C, ldc, F)) {
+        int launches = 0;
+        rc = dg_spmm_stream_launch(plan, val, B, ldb, C, ldc, F, alpha, beta, flags, row_scale, bias, scratch, stream, &launches);
+        g_kernel_launches.fetch_add(launches, std::memory_order_relaxed);
+    } else {
+        rc = dg_spmm_launch_rows(plan, val, B, ldb, C, ldc, F, alpha, beta, flags, row_scale, bias, scratch, stream);
     }
     if (profiled) {
         std::lock_guard<std::mutex> lock(g_profile.mu);
@@ -387,7 +403,7 @@ extern "C" int dg_spmm_csr(const dg_plan* plan, const float* val, const float* B
     int rc = dg_check_spmm_args(plan, val, B, ldb, C, ldc, F, flags, row_scale, bias);
     if (rc) return rc;
     dg_plan* p = const_cast<dg_plan*>(plan);
-    const int64_t need = (int64_t)p->n_chunks * F;
+    const int64_t need = dg_spmm_stream_eligible(plan, B, ldb, C, ldc, F) ? 2 * (int64_t)p->n_tasks * F : (int64_t)p->n_chunks * F;
     if (need > p->scratch_floats) {     // first use at this width: grow the plan's scratch (allocates, synchronises)
         DG_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
         cudaFree(p->scratch);

@@ -55,5 +55,5 @@ extern "C" int dg_spmm_csr_static(const dg_plan* plan, const float* val, const f
     if ((int64_t)plan->n_chunks * F > DG_STATIC_SCRATCH_FLOATS) return DG_ERR_SCRATCH;
     float* scratch = nullptr;
     if ((rc = static_scratch_address(plan->device, &scratch))) return rc;
-    return dg_spmm_launch(plan, val, B, ldb, C, ldc, F, alpha, beta, flags, row_scale, bias, scratch, (cudaStream_t)stream);
+    return dg_spmm_launch_rows(plan, val, B, ldb, C, ldc, F, alpha, beta, flags, row_scale, bias, scratch, (cudaStream_t)stream);
 }

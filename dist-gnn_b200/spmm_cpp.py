@@ -54,6 +54,8 @@ def lib():
             'dg_plan_destroy': ([vp], ctypes.c_int),
             'dg_plan_get_stats': ([vp, ctypes.POINTER(PlanStats)], ctypes.c_int),
             'dg_plan_copy_rowptr': ([vp, vp, vp], ctypes.c_int),
+            'dg_plan_set_task_size': ([vp, i32, vp], ctypes.c_int),
+            'dg_plan_device_status': ([vp, ctypes.POINTER(ctypes.c_int), vp], ctypes.c_int),
             'dg_spmm_csr': ([vp, vp, vp, i64, vp, i64, i32, f32, f32, u32, vp, vp, vp], ctypes.c_int),
             'dg_spmm_csr_static': ([vp, vp, vp, i64, vp, i64, i32, f32, f32, u32, vp, vp, vp], ctypes.c_int),
             'dg_static_scratch_capacity': ([], ctypes.c_int64),
@@ -131,6 +133,19 @@ class SpmmPlan:
         with torch.cuda.device(self.device):
             check(lib().dg_plan_copy_rowptr(self.handle, out.data_ptr(), _stream()))
         return out
+
+    def set_task_size(self, task_nnz):
+        """Entries per warp task of the streaming kernel (default 1024; <= 0 restores it)."""
+        with torch.cuda.device(self.device):
+            check(lib().dg_plan_set_task_size(self.handle, int(task_nnz), _stream()))
+        return self
+
+    def device_status(self):
+        """0, or non-zero if a kernel of this plan gave up on a bounded wait (its result is then invalid)."""
+        out = ctypes.c_int(-1)
+        with torch.cuda.device(self.device):
+            check(lib().dg_plan_device_status(self.handle, ctypes.byref(out), _stream()))
+        return out.value
 
     def spmm(self, B, C, alpha=1.0, beta=1.0, row_scale=None, bias=None, relu=False, values=None):
         """C <- epilogue(alpha * A @ B + beta * C) in place; B [k, F] and C [m, F] may be row-strided views."""

@@ -67,6 +67,12 @@ int dg_plan_create_ex(const int32_t* row, const int32_t* col, int64_t nnz, int32
                       int32_t heavy_threshold, int32_t chunk, void* stream, dg_plan** out);
 int dg_plan_destroy(dg_plan* plan);
 int dg_plan_get_stats(const dg_plan* plan, dg_plan_stats* host_out);
+/* The streaming kernel cuts the entry list into tasks of `task_nnz` entries (one warp each; default 1024).  This
+ * rebuilds the task tables for another size (<= 0 restores the default); synchronises `stream`. */
+int dg_plan_set_task_size(dg_plan* plan, int32_t task_nnz, void* stream);
+/* Reads the plan's device status word (synchronises `stream`): 0, or non-zero if a kernel gave up on one of its
+ * bounded waits for an asynchronous copy (the product's result is then invalid; nothing hangs). */
+int dg_plan_device_status(const dg_plan* plan, int* host_status, void* stream);
 /* copies the m+1 row offsets to host memory (synchronises `stream`); used to check CSR indexing bit for bit */
 int dg_plan_copy_rowptr(const dg_plan* plan, int64_t* host_rowptr, void* stream);
 

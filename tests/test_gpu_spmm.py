@@ -264,3 +264,43 @@ def test_15d_schedule_with_cuda_products_equals_1d_and_full_product(golden, P, c
         b = grp[0] // c
         assert_close(total.cpu().numpy(), full[b * n:(b + 1) * n], TOL, f'block {b} vs full product')
         assert_close(total.cpu().numpy(), oracle_15d[grp[0]], TOL, f'block {b} vs 1.5D oracle')
+
+
+@pytest.mark.parametrize('F', [64, 100, 128, 256, 300, 512, 1024])
+@pytest.mark.parametrize('task', [5, 32, 100, 0])
+def test_streaming_kernel_against_oracle(F, task):
+    """Widths whose rows are 16-byte aligned take the bulk-copy streaming kernel; small task sizes cut rows at many task
+    boundaries (carry rows + fix-up), 0 keeps the default.  Includes empty leading/trailing rows and a row spanning
+    dozens of tasks."""
+    rng = np.random.Generator(np.random.PCG64(1000 + F + task))
+    A = random_coo(rng, 261, 190, 3500, heavy=[(7, 150), (200, 190)])
+    keep = (A.row >= 3) & (A.row < 255) & (A.row != 100) & (A.row != 101)       # rows 0-2, 100-101, 255-260 are empty
+    A = ref_graph.Coo(A.row[keep], A.col[keep], A.val[keep], A.shape)
+    B = rng.standard_normal((190, F), dtype=np.float32)
+    C0 = rng.standard_normal((261, F), dtype=np.float32)
+    plan = make_plan(A).set_task_size(task)
+    for alpha, beta in ((1.0, 0.0), (0.75, -1.25)):
+        want = ref_gcn.spmm_coo(A, B, C0.copy(), alpha, beta)
+        C = dev(C0) if beta != 0 else torch.full((261, F), float('nan'), device='cuda')
+        plan.spmm(dev(B), C, alpha, beta)
+        assert_close(C.cpu().numpy(), want, TOL, f'F={F} task={task} beta={beta}')
+    assert plan.device_status() == 0
+
+
+def test_streaming_kernel_epilogue_and_reproducibility():
+    rng = np.random.Generator(np.random.PCG64(77))
+    A = random_coo(rng, 400, 300, 20000, heavy=[(0, 300), (399, 250)])
+    B = rng.standard_normal((300, 256), dtype=np.float32)
+    C0 = rng.standard_normal((400, 256), dtype=np.float32)
+    scale = rng.uniform(0.1, 2.0, 400).astype(np.float32)
+    bias = rng.standard_normal(256, dtype=np.float32)
+    want = ref_gcn.spmm_epilogue(A, B, C0, 1.0, 0.5, row_scale=scale, bias=bias, relu=True)
+    plan = make_plan(A).set_task_size(64)
+    outs = []
+    for _ in range(3):
+        C = dev(C0)
+        plan.spmm(dev(B), C, 1.0, 0.5, row_scale=dev(scale), bias=dev(bias), relu=True)
+        outs.append(C.cpu())
+    assert_close(outs[0].numpy(), want, TOL, 'streaming epilogue')
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    assert plan.device_status() == 0
