@@ -16,6 +16,7 @@
 // U entries are in flight per group before the first FMA, which is what keeps the memory system busy.
 #include <algorithm>
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 #include "dg_internal.h"
@@ -281,7 +282,11 @@ int launch_variant(const SpmmArgs& a, cudaStream_t stream)
 template <int VEC>
 int launch_vec(const SpmmArgs& a, cudaStream_t stream)
 {
-    const int nvec = a.nvec;
+    int nvec = a.nvec;
+    // Column tile: at most `cap` vectors of a row per pass over the entries (grid.y walks the tiles, and all CTAs of one
+    // tile are scheduled before the next tile's).  A narrower tile shrinks the slice of B that competes for the L2.
+    static const int cap = [] { const char* e = std::getenv("DG_ROWS_TILE_VECS"); return e && *e ? std::atoi(e) : 0; }();
+    if (cap > 0 && nvec > cap) nvec = cap;
     if (nvec <= 4) return launch_variant<VEC, 4, 1>(a, stream);
     if (nvec <= 8) return launch_variant<VEC, 8, 1>(a, stream);
     if (nvec <= 16) return launch_variant<VEC, 16, 1>(a, stream);

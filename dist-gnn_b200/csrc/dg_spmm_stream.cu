@@ -1,29 +1,31 @@
-// Streaming SpMM for sm_100a: the gathered rows of B are staged through shared memory by the bulk-copy engine.
+// Streaming SpMM for sm_100a: the gathered rows of B are staged through shared memory with asynchronous copies.
 //
 // Same product as the row kernels of dg_spmm.cu (C = epilogue(alpha * A * B + beta * C), replacing
 // cusparseSpMM at light_dist_gnn/spmm_cpp/spmm.cpp:26-28), for operands whose rows are 16-byte aligned and at
 // least 256 bytes wide.  What changes is how the memory system is driven:
 //   * the entry list of the block is cut into tasks of task_nnz entries regardless of row boundaries (perfect load
 //     balance, no separate heavy-row pass); one warp owns one task;
-//   * for every entry, ONE lane issues ONE cp.async.bulk that copies the whole needed piece of row col[e] of B
-//     (up to 1 KB) from global to the warp's ring of S stages in shared memory, completion counted on an mbarrier.
-//     Nothing is held in registers while the data is in flight, so a warp keeps ~56 KB outstanding instead of ~4 KB
-//     and an SM ~170 KB - the row kernels were bound by memory latency, not by DRAM or L2 bandwidth;
-//   * the warp then reads each staged row back with conflict-free 128-bit shared loads and accumulates in entry
-//     order (the order of the CPU oracle inside a row).
+//   * the warp copies the needed piece of row col[e] of B (up to 1 KB) straight from global to its ring of S stages
+//     in shared memory with 16-byte cp.async (L1 bypassed), one commit group per stage.  No register waits for data
+//     in flight, so a warp keeps tens of KB outstanding instead of ~4 KB - the row kernels were bound by memory
+//     latency, not by DRAM or L2 bandwidth;
+//   * it then reads each staged row back with conflict-free 128-bit shared loads and accumulates in entry order (the
+//     order of the CPU oracle inside a row).
 // Rows cut by a task boundary leave raw partial sums in two carry rows per task; k_stream_fixup adds them in task
 // order and applies the epilogue, so results stay bit-reproducible (no float atomics).
-// Every wait on an mbarrier is bounded: a warp that gives up sets the plan's status word, drains what it issued
-// (bounded again) and returns; the host can read the word with dg_plan_device_status.
+// Status: opt-in (dg_select_kernel(2) or DG_SPMM_KERNEL=stream).  Measured on B200, R-MAT 1 M nodes, degree 48, F = 256:
+// row kernels 5.86 ms, this kernel 6.83 ms at its best setting (2 stages x 4 rows, 24+ warps per SM); at degree 6 it is
+// 7 % faster (3.33 vs 3.57 ms).  A first version issued one cp.async.bulk per gathered row with mbarrier completion:
+// the bulk-copy engine sustained only about one row-sized copy per 100 cycles per SM (19.3 ms), so it is not used for
+// gathers.  A plain random 1 KB-row gather reaches 7.3 TB/s from HBM and 18.8 TB/s from L2 on this GPU; at the 54 % L2 hit
+// rate of these graphs that bounds any gather kernel near 10.9 TB/s, and the row kernels run at 9.2 TB/s.
+// Nothing in this kernel spins on a flag or barrier.
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
 #include "dg_internal.h"
 
 namespace {
-
-constexpr int kStages = 8;                 // ring depth per warp
-constexpr int kWaitLimit = 1 << 20;        // try_wait attempts before a warp gives up (each attempt can block a while)
 
 struct StreamArgs {
     const int64_t* rowptr;
@@ -36,48 +38,22 @@ struct StreamArgs {
     const int32_t* task_first_row;
     const dg_split_row* split;
     float* carry;                           // 2 * n_tasks rows of F floats
-    int* status;
     int64_t ldb, ldc, nnz;
     int32_t m, F, n_tasks, task_nnz;
     int32_t tile_floats;                    // floats of a B row handled by one column chunk (multiple of 4, <= 256)
-    int32_t rps;                            // entries (rows of B) per stage: 8, 16 or 32
+    int32_t rps;                            // entries (rows of B) per stage
     int32_t warp_bytes;                     // shared memory per warp
     float alpha, beta;
     uint32_t flags;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src)
 {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
-{
-    for (int i = 0; i < kWaitLimit; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
-__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 __device__ __forceinline__ float epilogue(const StreamArgs& a, float sum, float cold, int32_t row, int32_t colidx)
 {
@@ -89,8 +65,8 @@ __device__ __forceinline__ float epilogue(const StreamArgs& a, float sum, float 
     return out;
 }
 
-// One warp per task.  TPL = float4 per lane per staged row (1: pieces up to 512 B, 2: up to 1 KB).
-template <int TPL>
+// One warp per task.  TPL = float4 per lane per staged row (1: pieces up to 512 B, 2: up to 1 KB); S = ring depth.
+template <int TPL, int S>
 __global__ void __launch_bounds__(256) k_spmm_stream(const StreamArgs a)
 {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -99,23 +75,18 @@ __global__ void __launch_bounds__(256) k_spmm_stream(const StreamArgs a)
     if (t >= a.n_tasks) return;                         // no CTA-wide barrier below: a whole warp may leave
     const int chunk0 = blockIdx.y * a.tile_floats;      // first column of this column chunk
     const int piece = min(a.tile_floats, a.F - chunk0); // floats of each row this chunk handles (multiple of 4)
-    const uint32_t piece_bytes = (uint32_t)piece * 4u;
     const int tile_bytes = a.tile_floats * 4;
     const int rps = a.rps;
     unsigned char* base = smem_raw + (size_t)warp * a.warp_bytes;
     const uint32_t rows_s = smem_u32(base);
-    float* vals = reinterpret_cast<float*>(base + (size_t)kStages * rps * tile_bytes);
-    const uint32_t bars_s = smem_u32(vals + kStages * rps);
-    if (lane < kStages) mbar_init(bars_s + lane * 8, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    fence_async_proxy();
-    __syncwarp();
+    float* vals = reinterpret_cast<float*>(base + (size_t)S * rps * tile_bytes);
 
     const int64_t E0 = (int64_t)t * a.task_nnz;
     const int64_t E1 = min(E0 + (int64_t)a.task_nnz, a.nnz);
     const int nb = (int)((E1 - E0 + rps - 1) / rps);    // batches (= stage fills) of this task
     const bool act0 = lane * 4 < piece;
     const bool act1 = TPL == 2 && 128 + lane * 4 < piece;
+    const float* b_lane = a.B + chunk0 + lane * 4;
 
     // (col, val) of the entries, 32 at a time: group g covers E0 + 32 g .. + 31, one entry per lane
     int32_t c_cur = 0, c_nxt = 0;
@@ -127,24 +98,27 @@ __global__ void __launch_bounds__(256) k_spmm_stream(const StreamArgs a)
     load_group(0, c_cur, v_cur);
     load_group(1, c_nxt, v_nxt);
 
-    auto issue = [&](int b) {                           // fill stage b % S with batch b
-        const int s = b % kStages;
-        const int64_t eb = E0 + (int64_t)b * rps;
-        const int cnt = (int)min((int64_t)rps, E1 - eb);
-        const int off = (b * rps) & 31;                 // position of the batch inside its 32-entry group
-        const uint32_t bar = bars_s + s * 8;
-        if (lane == 0) mbar_expect_tx(bar, (uint32_t)cnt * piece_bytes);
-        const int j = lane - off;
-        if (j >= 0 && j < cnt) {
-            vals[s * rps + j] = v_cur;
-            bulk_copy_g2s(rows_s + (uint32_t)((s * rps + j) * tile_bytes), a.B + (size_t)c_cur * (size_t)a.ldb + chunk0,
-                          piece_bytes, bar);
+    auto issue = [&](int b) {                           // fill stage b % S with batch b; always exactly one commit group
+        if (b < nb) {
+            const int s = b % S;
+            const int64_t eb = E0 + (int64_t)b * rps;
+            const int cnt = (int)min((int64_t)rps, E1 - eb);
+            const int off = (b * rps) & 31;             // position of the batch inside its 32-entry group
+            const int j = lane - off;
+            if (j >= 0 && j < cnt) vals[s * rps + j] = v_cur;
+            uint32_t dst = rows_s + (uint32_t)(s * rps * tile_bytes) + lane * 16;
+            for (int k = 0; k < cnt; ++k, dst += tile_bytes) {
+                const int32_t c = __shfl_sync(0xffffffffu, c_cur, off + k);
+                const float* src = b_lane + (size_t)c * (size_t)a.ldb;
+                if (act0) cp_async16(dst, src);
+                if (TPL == 2 && act1) cp_async16(dst + 512u, src + 128);
+            }
+            if (off + rps >= 32) {                      // that was the last batch of the group: rotate, prefetch one more
+                c_cur = c_nxt; v_cur = v_nxt;
+                load_group((int64_t)(b * rps) / 32 + 2, c_nxt, v_nxt);
+            }
         }
-        if (off + rps >= 32) {                          // that was the last batch of the group: rotate, prefetch one more
-            c_cur = c_nxt; v_cur = v_nxt;
-            load_group((int64_t)(b * rps) / 32 + 2, c_nxt, v_nxt);
-        }
-        __syncwarp();
+        cp_async_commit();
     };
 
     // row bookkeeping: row r is being accumulated; its entries end at row_end; the ends of the next rows come from
@@ -156,9 +130,11 @@ __global__ void __launch_bounds__(256) k_spmm_stream(const StreamArgs a)
         return i <= a.m ? __ldg(a.rowptr + i) : INT64_MAX;
     };
     int64_t re_cur = load_ends(win), re_nxt = load_ends(win + 32);
-    int64_t row_end = __shfl_sync(0xffffffffu, re_cur, 0);
     bool began_before = __ldg(a.rowptr + r) < E0;       // the first row may have started in an earlier task
 
+    for (int b = 0; b < S; ++b) issue(b);               // prologue: S stages in flight
+
+    int64_t row_end = __shfl_sync(0xffffffffu, re_cur, 0);
     float4 acc0 = make_float4(0.f, 0.f, 0.f, 0.f), acc1 = make_float4(0.f, 0.f, 0.f, 0.f);
 
     auto store_row = [&](float* dst, int32_t row, bool raw) {   // dst points at column chunk0 of the target row
@@ -197,66 +173,43 @@ __global__ void __launch_bounds__(256) k_spmm_stream(const StreamArgs a)
     };
 
     if (t == 0)                                         // rows before the first entry are empty: they still get beta * C
-        for (int32_t rr = 0; rr < r; ++rr) {
-            store_row(a.C + (size_t)rr * (size_t)a.ldc + chunk0, rr, false);
-        }
+        for (int32_t rr = 0; rr < r; ++rr) store_row(a.C + (size_t)rr * (size_t)a.ldc + chunk0, rr, false);
 
-    const int prologue = min(nb, kStages);
-    for (int b = 0; b < prologue; ++b) issue(b);
-
-    bool gave_up = false;
-    int consumed = 0;
     for (int b = 0; b < nb; ++b) {
-        const int s = b % kStages;
-        const bool arrived = mbar_wait_bounded(bars_s + s * 8, (uint32_t)(b / kStages) & 1u);
-        if (!__all_sync(0xffffffffu, arrived)) { gave_up = true; break; }      // the whole warp stops together
-        consumed = b + 1;
+        cp_async_wait<S - 1>();                         // this lane's copies of batch b have landed ...
+        __syncwarp();                                   // ... and so have the other lanes'
+        const int s = b % S;
         const int64_t eb = E0 + (int64_t)b * rps;
         const int cnt = (int)min((int64_t)rps, E1 - eb);
-        const uint32_t stage_rows = rows_s + (uint32_t)(s * rps * tile_bytes) + lane * 16;
+        const unsigned char* stage_rows = base + (size_t)s * rps * tile_bytes + lane * 16;
         const float* stage_vals = vals + s * rps;
         for (int k = 0; k < cnt; ++k) {
             const int64_t e = eb + k;
             while (e == row_end && r < a.m) finish_row();
             const float v = stage_vals[k];
             if (act0) {
-                float4 x;
-                asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w)
-                             : "r"(stage_rows + (uint32_t)(k * tile_bytes)));
+                const float4 x = *reinterpret_cast<const float4*>(stage_rows + (size_t)k * tile_bytes);
                 acc0.x = fmaf(v, x.x, acc0.x); acc0.y = fmaf(v, x.y, acc0.y);
                 acc0.z = fmaf(v, x.z, acc0.z); acc0.w = fmaf(v, x.w, acc0.w);
             }
             if (TPL == 2 && act1) {
-                float4 x;
-                asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w)
-                             : "r"(stage_rows + (uint32_t)(k * tile_bytes) + 512u));
+                const float4 x = *reinterpret_cast<const float4*>(stage_rows + (size_t)k * tile_bytes + 512);
                 acc1.x = fmaf(v, x.x, acc1.x); acc1.y = fmaf(v, x.y, acc1.y);
                 acc1.z = fmaf(v, x.z, acc1.z); acc1.w = fmaf(v, x.w, acc1.w);
             }
         }
-        __syncwarp();
-        if (b + kStages < nb) {
-            fence_async_proxy();                        // our shared loads of this stage precede the engine's next writes
-            issue(b + kStages);
-        }
+        __syncwarp();                                   // every lane is done reading the stage before it is refilled
+        issue(b + S);
     }
-    if (gave_up) {
-        if (lane == 0) atomicExch(a.status, 1);
-        const int issued = min(nb, consumed + kStages);
-        for (int b = consumed; b < issued; ++b)         // drain what is still in flight before the CTA's memory is reused
-            mbar_wait_bounded(bars_s + (b % kStages) * 8, (uint32_t)(b / kStages) & 1u);
-        return;
-    }
+    cp_async_wait<0>();
     // end of the task: rows that end exactly here (and empty rows behind them), then the open row if it has entries here
     while (E1 == row_end && r < a.m) finish_row();
-    if (r < a.m) {
-        if (began_before || __ldg(a.rowptr + r) < E1)
-            store_row(a.carry + (size_t)(2 * (int64_t)t + (began_before ? 0 : 1)) * a.F + chunk0, r, true);
-    }
+    if (r < a.m && (began_before || __ldg(a.rowptr + r) < E1))
+        store_row(a.carry + (size_t)(2 * (int64_t)t + (began_before ? 0 : 1)) * a.F + chunk0, r, true);
 }
 
 // One CTA per row that spans tasks: carry pieces are added in task order, then the epilogue.
-__global__ void __launch_bounds__(128) k_stream_fixup(const StreamArgs a, int32_t n_split)
+__global__ void __launch_bounds__(128) k_stream_fixup(const StreamArgs a)
 {
     const dg_split_row sr = a.split[blockIdx.x];
     float* crow = a.C + (size_t)sr.row * (size_t)a.ldc;
@@ -268,22 +221,53 @@ __global__ void __launch_bounds__(128) k_stream_fixup(const StreamArgs a, int32_
     }
 }
 
-int g_kernel_choice = -1;   // -1 unread, 0 automatic, 1 row kernels only, 2 streaming whenever eligible
-
-int kernel_choice()
+int env_int(const char* name, int fallback)
 {
-    if (g_kernel_choice < 0) {
+    const char* e = std::getenv(name);
+    return e && *e ? std::atoi(e) : fallback;
+}
+
+struct Tuning {
+    int choice;     // 0 automatic, 1 row kernels only, 2 streaming whenever eligible
+    int stages;     // ring depth: 2, 4 or 8
+    int rps;        // entries per stage (0: derive from the row width)
+    int warps;      // warps per CTA (0: as many as shared memory allows, at most 8)
+};
+
+Tuning& tuning()
+{
+    static Tuning t = [] {
+        Tuning v{};
         const char* e = std::getenv("DG_SPMM_KERNEL");
-        g_kernel_choice = !e ? 0 : !std::strcmp(e, "rows") ? 1 : !std::strcmp(e, "stream") ? 2 : 0;
-    }
-    return g_kernel_choice;
+        v.choice = !e ? 0 : !std::strcmp(e, "rows") ? 1 : !std::strcmp(e, "stream") ? 2 : 0;
+        v.stages = env_int("DG_STREAM_STAGES", 2);
+        v.rps = env_int("DG_STREAM_RPS", 0);
+        v.warps = env_int("DG_STREAM_WARPS", 0);
+        return v;
+    }();
+    return t;
+}
+
+template <int TPL, int S>
+int launch_stream(const StreamArgs& a, dim3 grid, int threads, size_t smem, cudaStream_t stream)
+{
+    DG_CUDA(cudaFuncSetAttribute(k_spmm_stream<TPL, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    k_spmm_stream<TPL, S><<<grid, threads, smem, stream>>>(a);
+    return DG_OK;
 }
 
 }  // namespace
 
+extern "C" int dg_select_kernel(int family)
+{
+    if (family < 0 || family > 2) return DG_ERR_DIMS;
+    tuning().choice = family;
+    return DG_OK;
+}
+
 int dg_spmm_stream_eligible(const dg_plan* plan, const float* B, int64_t ldb, const float* C, int64_t ldc, int32_t F)
 {
-    if (kernel_choice() == 1) return 0;
+    if (tuning().choice != 2) return 0;      // opt-in: on B200 the row kernels are at least as fast (see the header comment)
     if (plan->n_tasks == 0 || !plan->task_first_row) return 0;
     if (F % 4 || ldb % 4 || ldc % 4 || F < 64) return 0;
     if (reinterpret_cast<uintptr_t>(B) % 16 || reinterpret_cast<uintptr_t>(C) % 16) return 0;
@@ -294,30 +278,32 @@ int dg_spmm_stream_launch(const dg_plan* plan, const float* val, const float* B,
                           int32_t F, float alpha, float beta, uint32_t flags, const float* row_scale, const float* bias,
                           float* scratch, cudaStream_t stream, int* launches)
 {
+    const Tuning& tune = tuning();
     StreamArgs a{};
     a.rowptr = plan->rowptr; a.col = plan->col; a.val = val; a.B = B; a.C = C;
     a.row_scale = row_scale; a.bias = bias; a.task_first_row = plan->task_first_row; a.split = plan->split;
-    a.carry = scratch; a.status = plan->status;
+    a.carry = scratch;
     a.ldb = ldb; a.ldc = ldc; a.nnz = plan->nnz; a.m = plan->m; a.F = F; a.n_tasks = plan->n_tasks; a.task_nnz = plan->task_nnz;
     a.alpha = alpha; a.beta = beta; a.flags = flags;
     a.tile_floats = std::min(F, 256);
     const int tile_bytes = a.tile_floats * 4;
-    a.rps = tile_bytes > 512 ? 8 : tile_bytes > 256 ? 16 : 32;
-    a.warp_bytes = ((kStages * a.rps * tile_bytes + kStages * a.rps * 4 + kStages * 8) + 127) / 128 * 128;
-    const int warps = std::max(1, std::min(8, (226 * 1024) / a.warp_bytes));
+    const int S = tune.stages == 2 || tune.stages == 8 ? tune.stages : 4;
+    a.rps = tune.rps > 0 ? tune.rps : (tile_bytes > 512 ? 4 : tile_bytes > 256 ? 8 : 16);
+    if (a.rps > 32) a.rps = 32;
+    while (32 % a.rps) --a.rps;                         // a batch must not straddle two 32-entry groups
+    a.warp_bytes = ((S * a.rps * tile_bytes + S * a.rps * 4) + 127) / 128 * 128;
+    int warps = std::max(1, std::min(8, (226 * 1024) / a.warp_bytes));
+    if (tune.warps > 0) warps = std::min(warps, tune.warps);
     const int col_chunks = (F + a.tile_floats - 1) / a.tile_floats;
     const size_t smem = (size_t)warps * a.warp_bytes;
     dim3 grid((unsigned)((plan->n_tasks + warps - 1) / warps), (unsigned)col_chunks);
-    if (tile_bytes > 512) {
-        DG_CUDA(cudaFuncSetAttribute(k_spmm_stream<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        k_spmm_stream<2><<<grid, warps * 32, smem, stream>>>(a);
-    } else {
-        DG_CUDA(cudaFuncSetAttribute(k_spmm_stream<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        k_spmm_stream<1><<<grid, warps * 32, smem, stream>>>(a);
-    }
+    int rc;
+    if (tile_bytes > 512) rc = S == 2 ? launch_stream<2, 2>(a, grid, warps * 32, smem, stream) : S == 8 ? launch_stream<2, 8>(a, grid, warps * 32, smem, stream) : launch_stream<2, 4>(a, grid, warps * 32, smem, stream);
+    else rc = S == 2 ? launch_stream<1, 2>(a, grid, warps * 32, smem, stream) : S == 8 ? launch_stream<1, 8>(a, grid, warps * 32, smem, stream) : launch_stream<1, 4>(a, grid, warps * 32, smem, stream);
+    if (rc) return rc;
     *launches = 1;
     if (plan->n_split > 0) {
-        k_stream_fixup<<<(unsigned)plan->n_split, 128, 0, stream>>>(a, plan->n_split);
+        k_stream_fixup<<<(unsigned)plan->n_split, 128, 0, stream>>>(a);
         *launches = 2;
     }
     return (int)cudaGetLastError();

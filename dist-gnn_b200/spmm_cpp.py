@@ -70,6 +70,7 @@ def lib():
             'dg_bcast_spmm_1d': ([vp, i32, vp, vp, vp, vp, i32, i32, vp, i32, vp, ctypes.c_int, vp], ctypes.c_int),
             'dg_bcast_spmm_15d': ([vp, vp, i32, vp, vp, vp, vp, i32, i32, vp, i32, vp, ctypes.c_int, vp], ctypes.c_int),
             'dg_comm_last_times': ([vp, ctypes.POINTER(StageTimes)], ctypes.c_int),
+            'dg_select_kernel': ([ctypes.c_int], ctypes.c_int),
             'dg_profile_begin': ([], ctypes.c_int),
             'dg_profile_end': ([ctypes.POINTER(Profile)], ctypes.c_int),
         }
@@ -182,6 +183,11 @@ class SpmmPlan:
         h, self.handle = getattr(self, 'handle', None), None
         if h and _lib is not None:
             _lib.dg_plan_destroy(h)
+
+
+def select_kernel(family):
+    """0 automatic (row kernels), 1 row kernels only, 2 streaming kernel where eligible; process-wide."""
+    check(lib().dg_select_kernel({'auto': 0, 'rows': 1, 'stream': 2}.get(family, family)))
 
 
 def profile_begin():

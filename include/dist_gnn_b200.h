@@ -70,8 +70,12 @@ int dg_plan_get_stats(const dg_plan* plan, dg_plan_stats* host_out);
 /* The streaming kernel cuts the entry list into tasks of `task_nnz` entries (one warp each; default 1024).  This
  * rebuilds the task tables for another size (<= 0 restores the default); synchronises `stream`. */
 int dg_plan_set_task_size(dg_plan* plan, int32_t task_nnz, void* stream);
-/* Reads the plan's device status word (synchronises `stream`): 0, or non-zero if a kernel gave up on one of its
- * bounded waits for an asynchronous copy (the product's result is then invalid; nothing hangs). */
+/* Kernel family of the local product: 0 = automatic (the row kernels), 1 = row kernels only, 2 = the streaming kernel
+ * (asynchronous copies through shared memory, entry-balanced tasks) wherever the operands allow it (rows of B and C
+ * 16-byte aligned and at least 64 floats wide).  Process-wide; also settable with DG_SPMM_KERNEL=rows|stream. */
+int dg_select_kernel(int family);
+/* Reads the plan's device status word (synchronises `stream`).  Reserved for kernels with bounded device-side waits;
+ * no current kernel waits on anything, so it reads 0. */
 int dg_plan_device_status(const dg_plan* plan, int* host_status, void* stream);
 /* copies the m+1 row offsets to host memory (synchronises `stream`); used to check CSR indexing bit for bit */
 int dg_plan_copy_rowptr(const dg_plan* plan, int64_t* host_rowptr, void* stream);

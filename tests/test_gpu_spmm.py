@@ -278,12 +278,17 @@ def test_streaming_kernel_against_oracle(F, task):
     A = ref_graph.Coo(A.row[keep], A.col[keep], A.val[keep], A.shape)
     B = rng.standard_normal((190, F), dtype=np.float32)
     C0 = rng.standard_normal((261, F), dtype=np.float32)
+    import spmm_cpp
     plan = make_plan(A).set_task_size(task)
-    for alpha, beta in ((1.0, 0.0), (0.75, -1.25)):
-        want = ref_gcn.spmm_coo(A, B, C0.copy(), alpha, beta)
-        C = dev(C0) if beta != 0 else torch.full((261, F), float('nan'), device='cuda')
-        plan.spmm(dev(B), C, alpha, beta)
-        assert_close(C.cpu().numpy(), want, TOL, f'F={F} task={task} beta={beta}')
+    spmm_cpp.select_kernel('stream')
+    try:
+        for alpha, beta in ((1.0, 0.0), (0.75, -1.25)):
+            want = ref_gcn.spmm_coo(A, B, C0.copy(), alpha, beta)
+            C = dev(C0) if beta != 0 else torch.full((261, F), float('nan'), device='cuda')
+            plan.spmm(dev(B), C, alpha, beta)
+            assert_close(C.cpu().numpy(), want, TOL, f'F={F} task={task} beta={beta}')
+    finally:
+        spmm_cpp.select_kernel('auto')
     assert plan.device_status() == 0
 
 
@@ -295,12 +300,17 @@ def test_streaming_kernel_epilogue_and_reproducibility():
     scale = rng.uniform(0.1, 2.0, 400).astype(np.float32)
     bias = rng.standard_normal(256, dtype=np.float32)
     want = ref_gcn.spmm_epilogue(A, B, C0, 1.0, 0.5, row_scale=scale, bias=bias, relu=True)
+    import spmm_cpp
     plan = make_plan(A).set_task_size(64)
     outs = []
-    for _ in range(3):
-        C = dev(C0)
-        plan.spmm(dev(B), C, 1.0, 0.5, row_scale=dev(scale), bias=dev(bias), relu=True)
-        outs.append(C.cpu())
+    spmm_cpp.select_kernel('stream')
+    try:
+        for _ in range(3):
+            C = dev(C0)
+            plan.spmm(dev(B), C, 1.0, 0.5, row_scale=dev(scale), bias=dev(bias), relu=True)
+            outs.append(C.cpu())
+    finally:
+        spmm_cpp.select_kernel('auto')
     assert_close(outs[0].numpy(), want, TOL, 'streaming epilogue')
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
     assert plan.device_status() == 0
