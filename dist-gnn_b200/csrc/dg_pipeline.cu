@@ -68,16 +68,21 @@ struct DeviceGuard {
     ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
 };
 
-int check_loop_args(int32_t n_stages, const int32_t* roots, const dg_plan* const* plans, const float* const* vals,
-                    const float* x_local, int32_t n, int32_t F, float* const* recv, int32_t nbuf, float* z, int nranks)
+// `group` consecutive stages share one product: plans[g] is n x (stages_in_group * n).
+int check_loop_args(int32_t n_stages, const int32_t* roots, int32_t group, const dg_plan* const* plans,
+                    const float* const* vals, const float* x_local, int32_t n, int32_t F, float* const* recv,
+                    int32_t nbuf, float* z, int nranks)
 {
-    if (n_stages < 0 || n < 0 || F < 0) return DG_ERR_DIMS;
+    if (n_stages < 0 || n < 0 || F < 0 || group < 1) return DG_ERR_DIMS;
+    if (nranks == 1 && group != 1) return DG_ERR_DIMS;
     if (n_stages > 0 && (!roots || !plans || !vals)) return DG_ERR_NULL;
     if ((int64_t)n * F > 0 && (!x_local || !z)) return DG_ERR_NULL;
-    for (int s = 0; s < n_stages; ++s) {
-        if (!plans[s]) return DG_ERR_NULL;
-        if (plans[s]->m != n || plans[s]->k != n) return DG_ERR_DIMS;
+    for (int s = 0; s < n_stages; ++s)
         if (roots[s] < 0 || roots[s] >= nranks) return DG_ERR_DIMS;
+    for (int g = 0; g * group < n_stages; ++g) {
+        const int in_group = n_stages - g * group < group ? n_stages - g * group : group;
+        if (!plans[g]) return DG_ERR_NULL;
+        if (plans[g]->m != n || (int64_t)plans[g]->k != (int64_t)in_group * n) return DG_ERR_DIMS;
     }
     if (nranks > 1) {
         if (nbuf < 2 || !recv) return DG_ERR_DIMS;
@@ -87,13 +92,14 @@ int check_loop_args(int32_t n_stages, const int32_t* roots, const dg_plan* const
     return DG_OK;
 }
 
-int stage_loop(dg_comm* comm, int32_t n_stages, const int32_t* roots, const dg_plan* const* plans,
+int stage_loop(dg_comm* comm, int32_t n_stages, const int32_t* roots, int32_t group, const dg_plan* const* plans,
                const float* const* vals, const float* x_local, int32_t n, int32_t F, float* const* recv, int32_t nbuf,
                float* z, int timed, cudaStream_t compute)
 {
     const int nranks = comm ? comm->nranks : 1;
-    int rc = check_loop_args(n_stages, roots, plans, vals, x_local, n, F, recv, nbuf, z, nranks);
+    int rc = check_loop_args(n_stages, roots, group, plans, vals, x_local, n, F, recv, nbuf, z, nranks);
     if (rc) return rc;
+    const int n_groups = (n_stages + group - 1) / group;
     const size_t count = (size_t)n * (size_t)F;
     if (n_stages == 0) {
         if (count) DG_CUDA(cudaMemsetAsync(z, 0, count * sizeof(float), compute));
@@ -111,32 +117,41 @@ int stage_loop(dg_comm* comm, int32_t n_stages, const int32_t* roots, const dg_p
     if ((rc = make_events(comm->ev_free, (size_t)nbuf, cudaEventDisableTiming))) return rc;
     comm->timed_stages = 0;
     if (timed) {
-        if ((rc = make_events(comm->t_comm, 2 * (size_t)n_stages, cudaEventDefault))) return rc;
-        if ((rc = make_events(comm->t_spmm, 2 * (size_t)n_stages, cudaEventDefault))) return rc;
+        if ((rc = make_events(comm->t_comm, 2 * (size_t)n_groups, cudaEventDefault))) return rc;
+        if ((rc = make_events(comm->t_spmm, 2 * (size_t)n_groups, cudaEventDefault))) return rc;
         DG_CUDA(cudaEventRecord(comm->t_begin, compute));
     }
     // Everything already queued on the compute stream (the producer of x_local, earlier readers of recv[]) comes first.
     DG_CUDA(cudaEventRecord(comm->ev_input, compute));
     DG_CUDA(cudaStreamWaitEvent(comm->side, comm->ev_input, 0));
-    for (int s = 0; s < n_stages; ++s) {
-        const int b = s % nbuf;
-        const bool is_root = roots[s] == comm->rank;
-        float* landing = is_root ? const_cast<float*>(x_local) : recv[b];
-        if (!is_root && s >= nbuf) DG_CUDA(cudaStreamWaitEvent(comm->side, comm->ev_free[b], 0));
-        if (timed) DG_CUDA(cudaEventRecord(comm->t_comm[2 * s], comm->side));
-        if (count) DG_NCCL(ncclBroadcast(x_local, landing, count, ncclFloat, roots[s], comm->comm, comm->side));
-        if (timed) DG_CUDA(cudaEventRecord(comm->t_comm[2 * s + 1], comm->side));
+    for (int g = 0; g < n_groups; ++g) {
+        const int b = g % nbuf;
+        const int s0 = g * group;
+        const int in_group = n_stages - s0 < group ? n_stages - s0 : group;
+        // a single-stage group rooted here is sent and read in place; wider groups gather every block (the root's
+        // too) side by side in the receive buffer, so that one product covers the whole group
+        const bool in_place = group == 1 && roots[s0] == comm->rank;
+        float* landing = in_place ? const_cast<float*>(x_local) : recv[b];
+        if (!in_place && g >= nbuf) DG_CUDA(cudaStreamWaitEvent(comm->side, comm->ev_free[b], 0));
+        if (timed) DG_CUDA(cudaEventRecord(comm->t_comm[2 * g], comm->side));
+        if (count) {
+            if (in_group > 1) DG_NCCL(ncclGroupStart());
+            for (int j = 0; j < in_group; ++j)
+                DG_NCCL(ncclBroadcast(x_local, landing + (size_t)j * count, count, ncclFloat, roots[s0 + j], comm->comm, comm->side));
+            if (in_group > 1) DG_NCCL(ncclGroupEnd());
+        }
+        if (timed) DG_CUDA(cudaEventRecord(comm->t_comm[2 * g + 1], comm->side));
         DG_CUDA(cudaEventRecord(comm->ev_arrived[b], comm->side));
         DG_CUDA(cudaStreamWaitEvent(compute, comm->ev_arrived[b], 0));
-        if (timed) DG_CUDA(cudaEventRecord(comm->t_spmm[2 * s], compute));
-        rc = dg_spmm_csr(plans[s], vals[s], landing, F, z, F, F, 1.f, s ? 1.f : 0.f, 0u, nullptr, nullptr, compute);
+        if (timed) DG_CUDA(cudaEventRecord(comm->t_spmm[2 * g], compute));
+        rc = dg_spmm_csr(plans[g], vals[g], landing, F, z, F, F, 1.f, g ? 1.f : 0.f, 0u, nullptr, nullptr, compute);
         if (rc) return rc;
-        if (timed) DG_CUDA(cudaEventRecord(comm->t_spmm[2 * s + 1], compute));
+        if (timed) DG_CUDA(cudaEventRecord(comm->t_spmm[2 * g + 1], compute));
         DG_CUDA(cudaEventRecord(comm->ev_free[b], compute));
     }
     if (timed) {
         DG_CUDA(cudaEventRecord(comm->t_end, compute));
-        comm->timed_stages = n_stages;
+        comm->timed_stages = n_groups;
     }
     return DG_OK;
 }
@@ -220,19 +235,19 @@ extern "C" int dg_comm_broadcast(dg_comm* c, float* buf, int64_t count, int root
     return DG_OK;
 }
 
-extern "C" int dg_bcast_spmm_1d(dg_comm* comm, int32_t n_stages, const int32_t* roots, const dg_plan* const* plans,
-                                const float* const* vals, const float* x_local, int32_t n, int32_t F,
-                                float* const* recv, int32_t nbuf, float* z, int timed, void* compute_stream)
+extern "C" int dg_bcast_spmm_1d(dg_comm* comm, int32_t n_stages, const int32_t* roots, int32_t group,
+                                const dg_plan* const* plans, const float* const* vals, const float* x_local, int32_t n,
+                                int32_t F, float* const* recv, int32_t nbuf, float* z, int timed, void* compute_stream)
 {
-    return stage_loop(comm, n_stages, roots, plans, vals, x_local, n, F, recv, nbuf, z, timed, (cudaStream_t)compute_stream);
+    return stage_loop(comm, n_stages, roots, group, plans, vals, x_local, n, F, recv, nbuf, z, timed, (cudaStream_t)compute_stream);
 }
 
 extern "C" int dg_bcast_spmm_15d(dg_comm* col_comm, dg_comm* row_comm, int32_t n_stages, const int32_t* roots,
-                                 const dg_plan* const* plans, const float* const* vals, const float* x_local,
-                                 int32_t n, int32_t F, float* const* recv, int32_t nbuf, float* z, int timed,
-                                 void* compute_stream)
+                                 int32_t group, const dg_plan* const* plans, const float* const* vals,
+                                 const float* x_local, int32_t n, int32_t F, float* const* recv, int32_t nbuf, float* z,
+                                 int timed, void* compute_stream)
 {
-    int rc = stage_loop(col_comm, n_stages, roots, plans, vals, x_local, n, F, recv, nbuf, z, timed, (cudaStream_t)compute_stream);
+    int rc = stage_loop(col_comm, n_stages, roots, group, plans, vals, x_local, n, F, recv, nbuf, z, timed, (cudaStream_t)compute_stream);
     if (rc) return rc;
     if (row_comm) rc = dg_comm_allreduce_sum(row_comm, z, (int64_t)n * F, compute_stream);
     return rc;

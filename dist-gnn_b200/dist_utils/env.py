@@ -24,7 +24,7 @@ from .timer import DistTimer
 class DistEnv:
     env = None
 
-    def __init__(self, rank, world_size, backend='nccl', rep=1):
+    def __init__(self, rank, world_size, backend='nccl', rep=1, stage_group=None):
         assert rank >= 0
         assert world_size > 0
         schedule.check_layout(world_size, rep)
@@ -37,6 +37,8 @@ class DistEnv:
         self.timer = DistTimer(self)
         self.store = dist.PrefixStore('dist_gnn_timer', dist.distributed_c10d._get_default_store())
         self._recv = {}
+        # stages fused into one product by the CUDA stage loop (1 = stage by stage, as the reference)
+        self.stage_group = max(1, int(stage_group if stage_group is not None else os.environ.get('DIST_GNN_STAGE_GROUP', 1)))
         DistEnv.env = self
 
     def __repr__(self):

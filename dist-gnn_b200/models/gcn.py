@@ -30,13 +30,44 @@ def broadcast(local_adj_parts, local_feature, tag):
     x = local_feature.contiguous()
     n, width = x.shape
     stages = env.stages()
-    plans = [spmm_cpp.plan_for(local_adj_parts[st.part]) for st in stages]
-    z = torch.empty_like(x)
     comm = env.col_comm
-    recv = env.recv_buffers(n, width) if comm is not None else None
+    group = min(env.stage_group, len(stages)) if comm is not None else 1
+    plans = group_plans(local_adj_parts, [st.part for st in stages], group)
+    z = torch.empty_like(x)
+    recv = env.recv_buffers(n * group, width) if comm is not None else None
     with env.timer.timing_cuda('broadcast+spmm'):
-        spmm_cpp.bcast_spmm(comm, [st.root_in_group for st in stages], plans, x, recv, z, row_comm=env.row_comm)
+        spmm_cpp.bcast_spmm(comm, [st.root_in_group for st in stages], plans, x, recv, z, row_comm=env.row_comm, group=group)
     return z
+
+
+_group_plan_cache = {}
+
+
+def group_plans(adj_parts, parts, group):
+    """Plans of the stage loop's products.  group = 1: one per column block, as the reference multiplies them.
+    group = k: the blocks of k consecutive stages are joined side by side into one n x (k*n) block (entries stay in
+    ascending (stage, column) order inside every row, so the sum order of the stage-by-stage loop is kept)."""
+    if group == 1:
+        return [spmm_cpp.plan_for(adj_parts[p]) for p in parts]
+    key = (id(adj_parts), tuple(parts), group)
+    hit = _group_plan_cache.get(key)
+    if hit is not None and hit[0] is adj_parts:
+        return hit[1]
+    plans = []
+    for g0 in range(0, len(parts), group):
+        blocks = [adj_parts[p] for p in parts[g0:g0 + group]]
+        n = blocks[0].size(0)
+        offsets, total = [], 0
+        for b in blocks:
+            offsets.append(total)
+            total += b.size(1)
+        row = torch.cat([b.indices()[0] for b in blocks])
+        col = torch.cat([b.indices()[1] + off for b, off in zip(blocks, offsets)])
+        val = torch.cat([b.values() for b in blocks])
+        order = torch.sort(row * total + col).indices
+        plans.append(spmm_cpp.SpmmPlan(row[order].to(torch.int32), col[order].to(torch.int32), val[order].contiguous(), n, total))
+    _group_plan_cache[key] = (adj_parts, plans)
+    return plans
 
 
 class DistGCNLayer(torch.autograd.Function):

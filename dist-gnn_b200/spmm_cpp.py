@@ -67,8 +67,8 @@ def lib():
             'dg_comm_rank': ([vp, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)], ctypes.c_int),
             'dg_comm_allreduce_sum': ([vp, vp, i64, vp], ctypes.c_int),
             'dg_comm_broadcast': ([vp, vp, i64, ctypes.c_int, vp], ctypes.c_int),
-            'dg_bcast_spmm_1d': ([vp, i32, vp, vp, vp, vp, i32, i32, vp, i32, vp, ctypes.c_int, vp], ctypes.c_int),
-            'dg_bcast_spmm_15d': ([vp, vp, i32, vp, vp, vp, vp, i32, i32, vp, i32, vp, ctypes.c_int, vp], ctypes.c_int),
+            'dg_bcast_spmm_1d': ([vp, i32, vp, i32, vp, vp, vp, i32, i32, vp, i32, vp, ctypes.c_int, vp], ctypes.c_int),
+            'dg_bcast_spmm_15d': ([vp, vp, i32, vp, i32, vp, vp, vp, i32, i32, vp, i32, vp, ctypes.c_int, vp], ctypes.c_int),
             'dg_comm_last_times': ([vp, ctypes.POINTER(StageTimes)], ctypes.c_int),
             'dg_select_kernel': ([ctypes.c_int], ctypes.c_int),
             'dg_profile_begin': ([], ctypes.c_int),
@@ -278,23 +278,26 @@ class Comm:
             _lib.dg_comm_destroy(h)
 
 
-def bcast_spmm(comm, roots, plans, x_local, recv, z, row_comm=None, timed=False):
-    """The pipelined stage loop (dg_bcast_spmm_1d / _15d): z <- sum_s plans[s] @ X_{roots[s]}.
+def bcast_spmm(comm, roots, plans, x_local, recv, z, row_comm=None, timed=False, group=1):
+    """The pipelined stage loop (dg_bcast_spmm_1d / _15d): z <- sum_s A_s @ X_{roots[s]}.
 
-    comm is a Comm or None (single rank); recv a list of >= 2 fp32 CUDA buffers with x_local's shape."""
+    comm is a Comm or None (single rank).  `group` consecutive stages share one product: plans[g] is the plan of the
+    joined sparse block of stages [g*group, (g+1)*group), and recv holds >= 2 fp32 CUDA buffers of group*n*F floats."""
     _dev_tensor(x_local, torch.float32, 'x_local'), _dev_tensor(z, torch.float32, 'z')
     n, F = x_local.shape
-    S = len(plans)
+    S = len(roots)
+    if len(plans) != (S + group - 1) // group:
+        raise RuntimeError(f'{S} stages in groups of {group} need {(S + group - 1) // group} plans, got {len(plans)}')
     roots_arr = (ctypes.c_int32 * max(S, 1))(*roots)
-    plan_arr = (ctypes.c_void_p * max(S, 1))(*[p.handle for p in plans])
-    val_arr = (ctypes.c_void_p * max(S, 1))(*[p.values.data_ptr() for p in plans])
+    plan_arr = (ctypes.c_void_p * max(len(plans), 1))(*[p.handle for p in plans])
+    val_arr = (ctypes.c_void_p * max(len(plans), 1))(*[p.values.data_ptr() for p in plans])
     recv = recv or []
     for b in recv:
         _dev_tensor(b, torch.float32, 'receive buffer')
-        if b.numel() < n * F:
-            raise RuntimeError('receive buffer smaller than one block')
+        if b.numel() < min(group, S) * n * F:
+            raise RuntimeError('receive buffer smaller than one group of blocks')
     recv_arr = (ctypes.c_void_p * max(len(recv), 1))(*[b.data_ptr() for b in recv])
-    args = (S, roots_arr, plan_arr, val_arr, x_local.data_ptr(), n, F, recv_arr, len(recv), z.data_ptr(), int(timed), _stream())
+    args = (S, roots_arr, group, plan_arr, val_arr, x_local.data_ptr(), n, F, recv_arr, len(recv), z.data_ptr(), int(timed), _stream())
     with torch.cuda.device(x_local.device):
         if row_comm is None:
             check(lib().dg_bcast_spmm_1d(comm.handle if comm else None, *args))

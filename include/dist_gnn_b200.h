@@ -132,20 +132,24 @@ typedef struct dg_stage_times {   /* device times of the last timed stage loop o
  * Replaces models/gcn.py:16-30.  For stage s the block of rank roots[s] (of `comm`) is broadcast on the
  * communicator's side stream into recv[s % nbuf] (the root sends `x_local` in place) while the compute stream
  * multiplies the block of stage s-1; events chain the two streams, nothing blocks the host.
- *   plans[s], vals[s]   plan and values of the sparse block multiplied at stage s (n x n)
- *   x_local             this rank's n x F block (read when this rank is a root, and never copied)
- *   recv[0..nbuf)       nbuf >= 2 device buffers of n*F floats owned by the caller
- *   z                   n x F result on the compute stream; overwritten (the first stage runs with beta = 0)
- *   timed != 0          record per-stage events; read them with dg_comm_last_times after synchronising
- * With a NULL comm or a single rank the loop degenerates to local products and no collective.  The summation order
- * is the reference's: stages in the order given, ascending column inside a row. */
-int dg_bcast_spmm_1d(dg_comm* comm, int32_t n_stages, const int32_t* host_roots,
+ *   group               stages fused into one product (>= 1).  With group = 1 this is the reference's loop stage for
+ *                       stage.  With group = k the broadcasts of k consecutive stages are issued as one NCCL group
+ *                       and land side by side in one receive buffer (k*n rows), and ONE product multiplies the joined
+ *                       n x (k*n) sparse block: fewer read-modify-write passes over z and longer rows per product,
+ *                       the same ascending (stage, column) summation order inside every row
+ *   plans[g], vals[g]   plan and values of the sparse block of product g = stages [g*group, (g+1)*group): n x (k_g*n)
+ *   x_local             this rank's n x F block (sent in place; with group = 1 also read in place, never copied)
+ *   recv[0..nbuf)       nbuf >= 2 device buffers of group*n*F floats owned by the caller
+ *   z                   n x F result on the compute stream; overwritten (the first product runs with beta = 0)
+ *   timed != 0          record per-product events; read them with dg_comm_last_times after synchronising
+ * With a NULL comm or a single rank the loop degenerates to local products and no collective (group must be 1). */
+int dg_bcast_spmm_1d(dg_comm* comm, int32_t n_stages, const int32_t* host_roots, int32_t group,
                      const dg_plan* const* host_plans, const float* const* host_vals,
                      const float* x_local, int32_t n, int32_t F, float* const* host_recv, int32_t nbuf,
                      float* z, int timed, void* compute_stream);
 /* 1.5D (dist_15d.py:61-106): the same loop inside the column communicator, then the sum of the partial z over
  * the row communicator (replication group). */
-int dg_bcast_spmm_15d(dg_comm* col_comm, dg_comm* row_comm, int32_t n_stages, const int32_t* host_roots,
+int dg_bcast_spmm_15d(dg_comm* col_comm, dg_comm* row_comm, int32_t n_stages, const int32_t* host_roots, int32_t group,
                       const dg_plan* const* host_plans, const float* const* host_vals,
                       const float* x_local, int32_t n, int32_t F, float* const* host_recv, int32_t nbuf,
                       float* z, int timed, void* compute_stream);
