@@ -40,6 +40,8 @@ def parse():
     ap.add_argument('--layers', type=int, default=0, help='override the number of GCN layers')
     ap.add_argument('--seed', type=int, default=0)
     ap.add_argument('--stage-group', type=int, default=0, help='stages fused into one product (0 = the default of DistEnv)')
+    ap.add_argument('--stage-order', default=None, choices=['reference', 'local_first'],
+                    help='order of the products inside a distributed SpMM (default: that of DistEnv)')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--profiler-range', action='store_true',
                     help='cudaProfilerStart/Stop around the device-resident timed steps (for ncu --profile-from-start off)')
@@ -140,16 +142,13 @@ def run_ours(args):
         raise SystemExit(f'--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}')
     if not torch.cuda.is_available():
         raise SystemExit('bench.py (impl ours) needs CUDA devices; there is no CPU path')
-    env = DistEnv(rank, world, 'nccl', rep=args.rep, stage_group=args.stage_group or None)
+    env = DistEnv(rank, world, 'nccl', rep=args.rep, stage_group=args.stage_group or None, stage_order=args.stage_order)
     cfg = workload_config(args)
     g = build_rank_graph(cfg, args, env)
     dims = [cfg['feat_dim']] + [cfg['hidden']] * (cfg['layers'] - 1) + [cfg['num_classes']]
     model = GCN(g, env, hidden_dim=cfg['hidden'], num_layers=cfg['layers'], weights=synthetic.glorot_weights(dims, args.seed))
     optimizer = torch.optim.Adam(model.parameters(), lr=0.01)
     loss_func = nn.CrossEntropyLoss()
-    from models.gcn import group_plans
-    stage_list = env.stages()                            # build every plan before anything is timed
-    group_plans(g.adj_parts, [st.part for st in stage_list], min(env.stage_group, len(stage_list)) if env.col_comm else 1)
     feat_host = g.features.cpu().pin_memory()            # e2e leg: the inputs start in pinned host memory
 
     def epoch_step():
@@ -217,7 +216,8 @@ def run_ours(args):
         'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
         'config': {'workload': describe(cfg, args, world), 'cache': 'inputs larger than L2 (adjacency + operands are GBs per rank); no flush',
                    'partition': '1d' if args.rep == 1 else f'1.5d(c={args.rep})', 'seed': args.seed,
-                   'vertex_permutation': not args.no_permute, 'final_loss': round(final_loss, 6)},
+                   'vertex_permutation': not args.no_permute, 'final_loss': round(final_loss, 6),
+                   'stage_order': env.stage_order, 'stage_group': env.stage_group},
         'roofline': {'bound': 'hbm', 'achieved': round(achieved, 2), 'peak': peaks['hbm_gbs'], 'unit': 'GB/s',
                      'frac': round(achieved / peaks['hbm_gbs'], 4), 'traffic': None, 'peak_source': peaks['source'],
                      'kernel': 'k_spmm_rows (+ split-row kernels), all local products of the slowest rank',
@@ -242,19 +242,23 @@ def measure_stage_loops(env, g, widths, spmm_cpp):
     """One timed distributed SpMM per width: broadcast bus GB/s, product time, and how much of the shorter of the two
     was hidden under the other:  overlap = (t_comm + t_spmm - t_loop) / min(t_comm, t_spmm)."""
     import torch.distributed as dist
-    from models.gcn import group_plans
+    from models.gcn import group_plans, ordered_products
     stages = env.stages()
     group = min(env.stage_group, len(stages))
-    plans = group_plans(g.adj_parts, [st.part for st in stages], group)
     roots = [st.root_in_group for st in stages]
     n = g.local_num_nodes
-    out = {'stage_group': group}
+    out = {'stage_group': group, 'stage_order': env.stage_order}
     for width in widths:
         x = torch.randn(n, width, device=env.device)
         z = torch.empty_like(x)
-        recv = env.recv_buffers(n * group, width)
         for timed in (False, True):
-            spmm_cpp.bcast_spmm(env.col_comm, roots, plans, x, recv, z, row_comm=env.row_comm, timed=timed, group=group)
+            if env.stage_order == 'local_first':
+                spmm_cpp.bcast_spmm_ordered(env.col_comm, *ordered_products(env, g.adj_parts, stages, x), x, z,
+                                            row_comm=env.row_comm, timed=timed, bcast_group=env.stage_group)
+            else:
+                plans = group_plans(g.adj_parts, [st.part for st in stages], group)
+                recv = env.recv_buffers(n * group, width)
+                spmm_cpp.bcast_spmm(env.col_comm, roots, plans, x, recv, z, row_comm=env.row_comm, timed=timed, group=group)
             torch.cuda.synchronize()
         t = env.col_comm.last_times()
         vals = torch.tensor([t['comm_ms'], t['spmm_ms'], t['total_ms']], dtype=torch.float64, device=env.device)

@@ -253,6 +253,91 @@ extern "C" int dg_bcast_spmm_15d(dg_comm* col_comm, dg_comm* row_comm, int32_t n
     return rc;
 }
 
+// Stage loop with a receive area for every remote block: all broadcasts are queued back to back on the side stream
+// (nothing ever waits for a buffer to be free), and the products run in the order the caller lists them - typically
+// this rank's own block first, which needs no transfer at all, then the remote blocks as they arrive.
+extern "C" int dg_bcast_spmm_ordered(dg_comm* comm, dg_comm* row_comm, int32_t n_stages, const int32_t* roots,
+                                     int32_t bcast_group, float* const* landing, int32_t n_products, const dg_plan* const* plans,
+                                     const float* const* vals, const float* const* operands, const int32_t* last_stage,
+                                     const float* x_local, int32_t n, int32_t F, float* z, int timed, void* compute_stream)
+{
+    cudaStream_t compute = (cudaStream_t)compute_stream;
+    if (!comm) return DG_ERR_NULL;
+    if (n_stages < 0 || n_products < 0 || n < 0 || F < 0 || bcast_group < 1) return DG_ERR_DIMS;
+    if ((n_stages > 0 && (!roots || !landing)) || (n_products > 0 && (!plans || !vals || !operands || !last_stage))) return DG_ERR_NULL;
+    const size_t count = (size_t)n * (size_t)F;
+    if (count && (!x_local || !z)) return DG_ERR_NULL;
+    for (int s = 0; s < n_stages; ++s) {
+        if (roots[s] < 0 || roots[s] >= comm->nranks) return DG_ERR_DIMS;
+        if (count && roots[s] != comm->rank && !landing[s]) return DG_ERR_NULL;
+    }
+    int prev = -1;
+    for (int p = 0; p < n_products; ++p) {      // products must consume the broadcasts in the order they are issued
+        if (!plans[p] || (count && !operands[p])) return DG_ERR_NULL;
+        if (plans[p]->m != n || last_stage[p] >= n_stages || (last_stage[p] >= 0 && last_stage[p] < prev)) return DG_ERR_DIMS;
+        if (last_stage[p] > prev) prev = last_stage[p];
+    }
+    int rc;
+    DeviceGuard guard(comm->device);
+    if ((rc = make_events(comm->ev_arrived, (size_t)n_products, cudaEventDisableTiming))) return rc;
+    comm->timed_stages = 0;
+    if (timed) {
+        if ((rc = make_events(comm->t_comm, 2 * (size_t)n_products, cudaEventDefault))) return rc;
+        if ((rc = make_events(comm->t_spmm, 2 * (size_t)n_products, cudaEventDefault))) return rc;
+        DG_CUDA(cudaEventRecord(comm->t_begin, compute));
+    }
+    if (n_products == 0 && count) DG_CUDA(cudaMemsetAsync(z, 0, count * sizeof(float), compute));
+    // the producer of x_local and every earlier reader of the landing area are already queued on the compute stream
+    DG_CUDA(cudaEventRecord(comm->ev_input, compute));
+    DG_CUDA(cudaStreamWaitEvent(comm->side, comm->ev_input, 0));
+    int issued = 0;                                 // broadcasts [0, issued) are on the side stream
+    // Broadcasts go out in NCCL groups of bcast_group consecutive stages, cut at the same places on every rank.
+    auto issue_until = [&](int until) -> int {
+        while (issued < until) {
+            const int end = issued + bcast_group < n_stages ? issued + bcast_group : n_stages;
+            if (count && comm->nranks > 1) {
+                if (end - issued > 1) DG_NCCL(ncclGroupStart());
+                for (int s = issued; s < end; ++s) {
+                    float* dst = roots[s] == comm->rank && !landing[s] ? const_cast<float*>(x_local) : landing[s];
+                    DG_NCCL(ncclBroadcast(x_local, dst, count, ncclFloat, roots[s], comm->comm, comm->side));
+                }
+                if (end - issued > 1) DG_NCCL(ncclGroupEnd());
+            }
+            issued = end;
+        }
+        return DG_OK;
+    };
+    for (int p = 0; p < n_products; ++p) {
+        if (timed) DG_CUDA(cudaEventRecord(comm->t_comm[2 * p], comm->side));
+        if (last_stage[p] >= issued && (rc = issue_until(last_stage[p] + 1))) return rc;
+        if (timed) DG_CUDA(cudaEventRecord(comm->t_comm[2 * p + 1], comm->side));
+        if (last_stage[p] >= 0) {
+            DG_CUDA(cudaEventRecord(comm->ev_arrived[p], comm->side));
+            DG_CUDA(cudaStreamWaitEvent(compute, comm->ev_arrived[p], 0));
+        }
+        if (timed) DG_CUDA(cudaEventRecord(comm->t_spmm[2 * p], compute));
+        rc = dg_spmm_csr(plans[p], vals[p], operands[p], F, z, F, F, 1.f, p ? 1.f : 0.f, 0u, nullptr, nullptr, compute);
+        if (rc) return rc;
+        if (timed) DG_CUDA(cudaEventRecord(comm->t_spmm[2 * p + 1], compute));
+    }
+    if (issued < n_stages) {    // broadcasts no product of this rank reads (it only roots them): still its part of the collective
+        if ((rc = issue_until(n_stages))) return rc;
+        // later work on the compute stream may overwrite x_local: it has to wait until the send has read it
+        if ((rc = make_events(comm->ev_free, 1, cudaEventDisableTiming))) return rc;
+        DG_CUDA(cudaEventRecord(comm->ev_free[0], comm->side));
+        DG_CUDA(cudaStreamWaitEvent(compute, comm->ev_free[0], 0));
+    }
+    if (row_comm) {
+        rc = dg_comm_allreduce_sum(row_comm, z, (int64_t)n * F, compute_stream);
+        if (rc) return rc;
+    }
+    if (timed) {
+        DG_CUDA(cudaEventRecord(comm->t_end, compute));
+        comm->timed_stages = n_products;
+    }
+    return DG_OK;
+}
+
 extern "C" int dg_comm_last_times(dg_comm* c, dg_stage_times* out)
 {
     if (!c || !out) return DG_ERR_NULL;

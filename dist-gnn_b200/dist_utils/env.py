@@ -24,7 +24,7 @@ from .timer import DistTimer
 class DistEnv:
     env = None
 
-    def __init__(self, rank, world_size, backend='nccl', rep=1, stage_group=None):
+    def __init__(self, rank, world_size, backend='nccl', rep=1, stage_group=None, stage_order=None):
         assert rank >= 0
         assert world_size > 0
         schedule.check_layout(world_size, rep)
@@ -39,6 +39,11 @@ class DistEnv:
         self._recv = {}
         # stages fused into one product by the CUDA stage loop (1 = stage by stage, as the reference)
         self.stage_group = max(1, int(stage_group if stage_group is not None else os.environ.get('DIST_GNN_STAGE_GROUP', 1)))
+        # 'reference': products in ascending stage order (the reference's sum order), two receive buffers;
+        # 'local_first': own block first, one receive area for all remote blocks, every broadcast queued up front
+        self.stage_order = stage_order if stage_order is not None else os.environ.get('DIST_GNN_STAGE_ORDER', 'reference')
+        if self.stage_order not in ('reference', 'local_first'):
+            raise ValueError(f'unknown stage order {self.stage_order!r}')
         DistEnv.env = self
 
     def __repr__(self):

@@ -31,13 +31,39 @@ def broadcast(local_adj_parts, local_feature, tag):
     n, width = x.shape
     stages = env.stages()
     comm = env.col_comm
+    z = torch.empty_like(x)
+    if comm is not None and env.stage_order == 'local_first':
+        with env.timer.timing_cuda('broadcast+spmm'):
+            spmm_cpp.bcast_spmm_ordered(comm, *ordered_products(env, local_adj_parts, stages, x), x, z,
+                                        row_comm=env.row_comm, bcast_group=env.stage_group)
+        return z
     group = min(env.stage_group, len(stages)) if comm is not None else 1
     plans = group_plans(local_adj_parts, [st.part for st in stages], group)
-    z = torch.empty_like(x)
     recv = env.recv_buffers(n * group, width) if comm is not None else None
     with env.timer.timing_cuda('broadcast+spmm'):
         spmm_cpp.bcast_spmm(comm, [st.root_in_group for st in stages], plans, x, recv, z, row_comm=env.row_comm, group=group)
     return z
+
+
+def ordered_products(env, adj_parts, stages, x):
+    """Arguments (roots, landing, products) of spmm_cpp.bcast_spmm_ordered for the 'local_first' stage order: the block
+    this rank roots is multiplied first, straight from x; the remote blocks land side by side in one receive area,
+    in broadcast order, and are multiplied env.stage_group at a time as they arrive."""
+    me = env.col_comm.rank
+    n, width = x.shape
+    remote = [i for i, st in enumerate(stages) if st.root_in_group != me]
+    own = [i for i, st in enumerate(stages) if st.root_in_group == me]
+    area = env.recv_buffers(max(len(remote), 1) * n, width, nbuf=1)[0]
+    landing = [None] * len(stages)
+    for pos, i in enumerate(remote):
+        landing[i] = area[pos * n:(pos + 1) * n]
+    products = [(spmm_cpp.plan_for(adj_parts[stages[i].part]), x, -1) for i in own]
+    group = max(1, min(env.stage_group, len(remote)))
+    plans = group_plans(adj_parts, [stages[i].part for i in remote], group) if remote else []
+    for g, plan in enumerate(plans):
+        members = remote[g * group:(g + 1) * group]
+        products.append((plan, area[g * group * n:(g * group + len(members)) * n], members[-1]))
+    return [st.root_in_group for st in stages], landing, products
 
 
 _group_plan_cache = {}

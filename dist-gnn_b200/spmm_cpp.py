@@ -69,6 +69,7 @@ def lib():
             'dg_comm_broadcast': ([vp, vp, i64, ctypes.c_int, vp], ctypes.c_int),
             'dg_bcast_spmm_1d': ([vp, i32, vp, i32, vp, vp, vp, i32, i32, vp, i32, vp, ctypes.c_int, vp], ctypes.c_int),
             'dg_bcast_spmm_15d': ([vp, vp, i32, vp, i32, vp, vp, vp, i32, i32, vp, i32, vp, ctypes.c_int, vp], ctypes.c_int),
+            'dg_bcast_spmm_ordered': ([vp, vp, i32, vp, i32, vp, i32, vp, vp, vp, vp, vp, i32, i32, vp, ctypes.c_int, vp], ctypes.c_int),
             'dg_comm_last_times': ([vp, ctypes.POINTER(StageTimes)], ctypes.c_int),
             'dg_select_kernel': ([ctypes.c_int], ctypes.c_int),
             'dg_profile_begin': ([], ctypes.c_int),
@@ -303,4 +304,30 @@ def bcast_spmm(comm, roots, plans, x_local, recv, z, row_comm=None, timed=False,
             check(lib().dg_bcast_spmm_1d(comm.handle if comm else None, *args))
         else:
             check(lib().dg_bcast_spmm_15d(comm.handle if comm else None, row_comm.handle, *args))
+    return z
+
+
+def bcast_spmm_ordered(comm, roots, landing, products, x_local, z, row_comm=None, timed=False, bcast_group=1):
+    """dg_bcast_spmm_ordered: every broadcast queued up front, products in the given order.
+
+    roots[s]     root (rank inside comm) of broadcast s; the same list on every rank
+    landing[s]   fp32 CUDA tensor (n x F) receiving block s here, or None at a stage this rank roots
+    products     list of (plan, operand tensor, last_stage): operand is x_local or a (k*n) x F view of the landing area,
+                 last_stage the index of the last broadcast the product reads (-1: none)"""
+    _dev_tensor(x_local, torch.float32, 'x_local'), _dev_tensor(z, torch.float32, 'z')
+    n, F = x_local.shape
+    S, P = len(roots), len(products)
+    roots_arr = (ctypes.c_int32 * max(S, 1))(*roots)
+    land_arr = (ctypes.c_void_p * max(S, 1))(*[None if t is None else _dev_tensor(t, torch.float32, 'landing block').data_ptr() for t in landing])
+    plan_arr = (ctypes.c_void_p * max(P, 1))(*[p.handle for p, _, _ in products])
+    val_arr = (ctypes.c_void_p * max(P, 1))(*[p.values.data_ptr() for p, _, _ in products])
+    for plan, operand, _ in products:
+        _dev_tensor(operand, torch.float32, 'operand')
+        if operand.size(0) != plan.k or operand.size(1) != F:
+            raise RuntimeError(f'operand {tuple(operand.shape)} does not match a plan with {plan.k} columns and width {F}')
+    op_arr = (ctypes.c_void_p * max(P, 1))(*[t.data_ptr() for _, t, _ in products])
+    last_arr = (ctypes.c_int32 * max(P, 1))(*[l for _, _, l in products])
+    with torch.cuda.device(x_local.device):
+        check(lib().dg_bcast_spmm_ordered(comm.handle, row_comm.handle if row_comm else None, S, roots_arr, bcast_group, land_arr, P, plan_arr,
+                                          val_arr, op_arr, last_arr, x_local.data_ptr(), n, F, z.data_ptr(), int(timed), _stream()))
     return z

@@ -153,6 +153,25 @@ int dg_bcast_spmm_15d(dg_comm* col_comm, dg_comm* row_comm, int32_t n_stages, co
                       const dg_plan* const* host_plans, const float* const* host_vals,
                       const float* x_local, int32_t n, int32_t F, float* const* host_recv, int32_t nbuf,
                       float* z, int timed, void* compute_stream);
+/* The same distributed product with a receive area for every remote block and the products in the caller's order
+ * (replaces gcn.py:16-30 / dist_15d.py:61-106 like the two functions above).  All n_stages broadcasts are queued back to
+ * back on the side stream in the order of host_roots - the same on every rank - and never wait for a buffer; the
+ * products run on the compute stream in the order listed, each as soon as broadcast host_last_stage[p] (an index into
+ * host_roots, -1 = needs no transfer) has landed.  Listing this rank's own block first starts the arithmetic while the
+ * first transfer is still in flight; the price is (n_stages - 1) * n * F floats of receive area and a per-rank sum
+ * order (own block first) that differs from the reference's ascending order by rounding only.
+ *   bcast_group         consecutive broadcasts issued as one NCCL group (>= 1; the same value on every rank)
+ *   host_landing[s]     where the block of stage s lands on this rank (n*F floats); NULL at a stage this rank roots
+ *                       means "send from x_local, keep no second copy"
+ *   host_plans/vals[p]  sparse block of product p: n x (rows of its operand); host_operands[p] its dense operand:
+ *                       x_local, or a pointer into the landing area where the blocks it covers lie side by side
+ *   host_last_stage     non-decreasing over the products that need transfers, and its maximum is n_stages - 1
+ *   row_comm            NULL, or the 1.5D replication group over which the finished z is summed */
+int dg_bcast_spmm_ordered(dg_comm* comm, dg_comm* row_comm, int32_t n_stages, const int32_t* host_roots,
+                          int32_t bcast_group, float* const* host_landing, int32_t n_products, const dg_plan* const* host_plans,
+                          const float* const* host_vals, const float* const* host_operands,
+                          const int32_t* host_last_stage, const float* x_local, int32_t n, int32_t F, float* z,
+                          int timed, void* compute_stream);
 int dg_comm_last_times(dg_comm* comm, dg_stage_times* host_out);
 
 /* ---- instrumentation (no counterpart in the reference, whose timer synchronises the device around every call,

@@ -54,6 +54,11 @@ def _worker(rank, world, rep, port, out_dir, mode):
                 env.stage_group = 2          # the same loop with two stages fused into one product
                 rec[f'zg{i}'] = broadcast(g.adj_parts, x, f'w{width}').cpu().numpy()
                 env.stage_group = 1
+                env.stage_order = 'local_first'   # own block first, every broadcast queued up front
+                rec[f'zl{i}'] = broadcast(g.adj_parts, x, f'w{width}').cpu().numpy()
+                env.stage_group = 2
+                rec[f'zlg{i}'] = broadcast(g.adj_parts, x, f'w{width}').cpu().numpy()
+                env.stage_group, env.stage_order = 1, 'reference'
         torch.cuda.synchronize()
         np.savez(os.path.join(out_dir, f'rank{rank}.npz'), **rec)
     finally:
@@ -97,7 +102,8 @@ def test_back_to_back_stage_loops_at_two_ranks(golden):
         want = ref_gcn.broadcast_1d([p['adj_parts'] for p in parts], [res[r][f'x{i}'] for r in range(2)])
         for r in range(2):
             assert_close(res[r][f'z{i}'], want[r], 1e-5, f'loop {i} rank {r}')
-            assert_close(res[r][f'zg{i}'], want[r], 1e-5, f'fused-stage loop {i} rank {r}')
+            for key in ('zg', 'zl', 'zlg'):
+                assert_close(res[r][f'{key}{i}'], want[r], 1e-5, f'{key} loop {i} rank {r}')
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason='needs 4 GPUs')
@@ -109,4 +115,5 @@ def test_15d_stage_loop_at_four_ranks(golden):
         want = ref_gcn.broadcast_15d([p['adj_parts'] for p in parts], [res[b * 2][f'x{i}'] for b in range(2)], 4, 2)
         for r in range(4):
             assert_close(res[r][f'z{i}'], want[r], 1e-5, f'loop {i} rank {r}')
-            assert_close(res[r][f'zg{i}'], want[r], 1e-5, f'fused-stage loop {i} rank {r}')
+            for key in ('zg', 'zl', 'zlg'):
+                assert_close(res[r][f'{key}{i}'], want[r], 1e-5, f'{key} loop {i} rank {r}')
