@@ -42,6 +42,8 @@ def parse():
     ap.add_argument('--stage-group', type=int, default=0, help='stages fused into one product (0 = the default of DistEnv)')
     ap.add_argument('--stage-order', default=None, choices=['reference', 'local_first'],
                     help='order of the products inside a distributed SpMM (default: that of DistEnv)')
+    ap.add_argument('--dense', default=None, choices=['fp32', '3xtf32'],
+                    help='dense transform: fp32 library GEMM, or three tensor-core TF32 passes with fp32 accumulation')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--profiler-range', action='store_true',
                     help='cudaProfilerStart/Stop around the device-resident timed steps (for ncu --profile-from-start off)')
@@ -143,6 +145,9 @@ def run_ours(args):
     if not torch.cuda.is_available():
         raise SystemExit('bench.py (impl ours) needs CUDA devices; there is no CPU path')
     env = DistEnv(rank, world, 'nccl', rep=args.rep, stage_group=args.stage_group or None, stage_order=args.stage_order)
+    import models.gcn as gcn_module
+    if args.dense:
+        gcn_module.DENSE_MODE = args.dense
     cfg = workload_config(args)
     g = build_rank_graph(cfg, args, env)
     dims = [cfg['feat_dim']] + [cfg['hidden']] * (cfg['layers'] - 1) + [cfg['num_classes']]
@@ -217,7 +222,7 @@ def run_ours(args):
         'config': {'workload': describe(cfg, args, world), 'cache': 'inputs larger than L2 (adjacency + operands are GBs per rank); no flush',
                    'partition': '1d' if args.rep == 1 else f'1.5d(c={args.rep})', 'seed': args.seed,
                    'vertex_permutation': not args.no_permute, 'final_loss': round(final_loss, 6),
-                   'stage_order': env.stage_order, 'stage_group': env.stage_group},
+                   'stage_order': env.stage_order, 'stage_group': env.stage_group, 'dense': gcn_module.DENSE_MODE},
         'roofline': {'bound': 'hbm', 'achieved': round(achieved, 2), 'peak': peaks['hbm_gbs'], 'unit': 'GB/s',
                      'frac': round(achieved / peaks['hbm_gbs'], 4), 'traffic': None, 'peak_source': peaks['source'],
                      'kernel': 'k_spmm_rows (+ split-row kernels), all local products of the slowest rank',

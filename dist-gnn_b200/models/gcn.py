@@ -9,6 +9,8 @@ the reuse of the un-transposed row block of A in backward, which is exact only f
 
 There is no CPU implementation: CPU tensors raise.
 """
+import os
+
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
@@ -21,6 +23,40 @@ def spmm(A, B, C):
     """C += A @ B in place for a sparse COO block A (the binding of gcn.py:9-13, on a cached plan)."""
     spmm_cpp.plan_for(A).spmm(B, C, 1.0, 1.0)
     return C
+
+
+# How the dense transforms around the SpMM (torch.mm at gcn.py:41, :49-50) are computed:
+#   'fp32'    plain fp32 library GEMM (CUDA cores), bit-for-bit what the reference's torch.mm does on a GPU
+#   '3xtf32'  each fp32 operand is cut into a TF32-exact head and its residual, and the product is accumulated in fp32
+#             from three tensor-core TF32 GEMMs  head*head + head*tail + tail*head  (the tail*tail term, 2^-22 relative,
+#             is dropped).  About 5e-7 relative error per product - inside the 1e-5 parity bound - at a fraction of the
+#             CUDA-core time, because these skinny GEMMs are then bound by reading the activations.
+DENSE_MODE = os.environ.get('DIST_GNN_DENSE', 'fp32')
+
+
+def _tf32_split(x):
+    head = (x.contiguous().view(torch.int32) & -8192).view(torch.float32)    # sign, exponent, top 10 mantissa bits
+    return head, x - head
+
+
+def dense_mm(a, b, ta=False, tb=False):
+    """op(a) @ op(b) for fp32 CUDA matrices according to DENSE_MODE; ta / tb transpose the (contiguous) operand."""
+    if DENSE_MODE != '3xtf32' or not a.is_cuda:
+        return torch.mm(a.t() if ta else a, b.t() if tb else b)
+    (ah, at), (bh, bt) = _tf32_split(a), _tf32_split(b)
+    if ta:
+        ah, at = ah.t(), at.t()
+    if tb:
+        bh, bt = bh.t(), bt.t()
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        out = torch.mm(ah, bh)
+        out.addmm_(ah, bt)
+        out.addmm_(at, bh)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    return out
 
 
 def broadcast(local_adj_parts, local_feature, tag):
@@ -103,7 +139,7 @@ class DistGCNLayer(torch.autograd.Function):
         ctx.adj_parts, ctx.tag = adj_parts, tag
         z_local = broadcast(adj_parts, features, 'Forward' + tag)
         with DistEnv.env.timer.timing_cuda('mm'):
-            z_local = torch.mm(z_local, weight)
+            z_local = dense_mm(z_local, weight)
         return z_local
 
     @staticmethod
@@ -111,8 +147,8 @@ class DistGCNLayer(torch.autograd.Function):
         features, weight = ctx.saved_tensors
         ag = broadcast(ctx.adj_parts, grad_output, 'Backward' + ctx.tag)
         with DistEnv.env.timer.timing_cuda('mm'):
-            grad_features = torch.mm(ag, weight.t()) if ctx.needs_input_grad[0] else None
-            grad_weight = torch.mm(features.t(), ag)
+            grad_features = dense_mm(ag, weight, tb=True) if ctx.needs_input_grad[0] else None
+            grad_weight = dense_mm(features, ag, ta=True)
         with DistEnv.env.timer.timing_cuda('all_reduce'):
             DistEnv.env.all_reduce_sum(grad_weight)
         return grad_features, grad_weight, None, None

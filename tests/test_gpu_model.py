@@ -92,6 +92,39 @@ def test_cpu_tensors_are_refused(golden, env1):
         broadcast(g.adj_parts, g.features, 't')
 
 
+def test_three_pass_tf32_dense_transform_stays_inside_the_parity_bound(golden, env1, monkeypatch):
+    """The tensor-core dense transform (three TF32 GEMMs per product, fp32 accumulation) against float64 and, through a
+    whole layer forward/backward, against the fp32 path: 1e-5 relative per tensor like every other parity check."""
+    import models.gcn as gcn
+    g = torch.Generator(device='cuda').manual_seed(3)
+    a = torch.randn(20000, 256, device='cuda', generator=g)
+    b = torch.randn(256, 256, device='cuda', generator=g)
+    c = torch.randn(20000, 47, device='cuda', generator=g)
+    monkeypatch.setattr(gcn, 'DENSE_MODE', '3xtf32')
+    for got, want in ((gcn.dense_mm(a, b), a.double() @ b.double()),
+                      (gcn.dense_mm(a, b, tb=True), a.double() @ b.double().t()),
+                      (gcn.dense_mm(a, c, ta=True), a.double().t() @ c.double())):
+        assert_close(got.cpu().numpy(), want.cpu().numpy(), TOL, 'dense transform vs float64')
+    # one-pass TF32 would not pass: make sure the bound is meaningful
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        one_pass = torch.mm(a, b)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = False
+    err = (one_pass.double() - a.double() @ b.double()).abs().max().item() / (a.double() @ b.double()).abs().max().item()
+    assert err > TOL
+    # and a short training run keeps matching the fp32 path
+    import dist_train
+    from coo_graph import COO_Graph, Parted_COO_Graph
+    z = golden('graph_small')
+    graph = Parted_COO_Graph.from_full(COO_Graph.from_dict('gsmall', _fixture_dataset(z), device='cuda'), 0, 1)
+    _, losses_tc = dist_train.train(graph, env1, total_epoch=3, hidden_dim=16, num_layers=3)
+    monkeypatch.setattr(gcn, 'DENSE_MODE', 'fp32')
+    _, losses_fp32 = dist_train.train(graph, env1, total_epoch=3, hidden_dim=16, num_layers=3)
+    for x, y in zip(losses_tc, losses_fp32):
+        assert abs(x - y) <= 2e-5 * max(1.0, abs(y))
+
+
 @pytest.fixture(scope='module')
 def big_graph():
     """The 2,449,029-node / 123.7 M-edge benchmark graph, generated and normalised on the GPU."""
