@@ -40,8 +40,9 @@ def parse():
     ap.add_argument('--layers', type=int, default=0, help='override the number of GCN layers')
     ap.add_argument('--seed', type=int, default=0)
     ap.add_argument('--stage-group', type=int, default=0, help='stages fused into one product (0 = the default of DistEnv)')
-    ap.add_argument('--stage-order', default=None, choices=['reference', 'local_first'],
+    ap.add_argument('--stage-order', default=None, choices=['reference', 'local_first', 'feature_chunks'],
                     help='order of the products inside a distributed SpMM (default: that of DistEnv)')
+    ap.add_argument('--chunk-width', type=int, default=0, help='column chunk width of the feature_chunks order (0 = default 64)')
     ap.add_argument('--dense', default=None, choices=['fp32', '3xtf32'],
                     help='dense transform: fp32 library GEMM, or three tensor-core TF32 passes with fp32 accumulation')
     ap.add_argument('--no-cpu-baseline', action='store_true')
@@ -145,6 +146,8 @@ def run_ours(args):
     if not torch.cuda.is_available():
         raise SystemExit('bench.py (impl ours) needs CUDA devices; there is no CPU path')
     env = DistEnv(rank, world, 'nccl', rep=args.rep, stage_group=args.stage_group or None, stage_order=args.stage_order)
+    if args.chunk_width:
+        env.chunk_width = args.chunk_width
     import models.gcn as gcn_module
     if args.dense:
         gcn_module.DENSE_MODE = args.dense
@@ -257,7 +260,12 @@ def measure_stage_loops(env, g, widths, spmm_cpp):
         x = torch.randn(n, width, device=env.device)
         z = torch.empty_like(x)
         for timed in (False, True):
-            if env.stage_order == 'local_first':
+            if env.stage_order == 'feature_chunks' and env.rep == 1:
+                plan = group_plans(g.adj_parts, [st.part for st in stages], len(stages))[0]
+                chunks = spmm_cpp.chunk_widths(width, env.chunk_width)
+                spmm_cpp.allgather_spmm(env.col_comm, plan, x, env.recv_buffers(n, max(chunks), tag='pack'),
+                                        env.recv_buffers(n * env.col_comm.size, max(chunks), tag='area'), z, chunks, timed=timed)
+            elif env.stage_order == 'local_first':
                 spmm_cpp.bcast_spmm_ordered(env.col_comm, *ordered_products(env, g.adj_parts, stages, x), x, z,
                                             row_comm=env.row_comm, timed=timed, bcast_group=env.stage_group)
             else:

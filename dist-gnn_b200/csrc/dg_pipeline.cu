@@ -26,6 +26,7 @@ struct dg_comm {
     cudaEvent_t ev_input;                    // this rank's block is ready on the compute stream
     std::vector<cudaEvent_t> ev_arrived;     // per receive buffer: broadcast into it finished
     std::vector<cudaEvent_t> ev_free;        // per receive buffer: the product that read it finished
+    std::vector<cudaEvent_t> ev_packed;      // per pack buffer: the column chunk to send is ready
     std::vector<cudaEvent_t> t_comm, t_spmm; // timing pairs per stage (2 events each)
     cudaEvent_t t_begin, t_end;
     int timed_stages;
@@ -197,7 +198,7 @@ extern "C" int dg_comm_destroy(dg_comm* c)
     DeviceGuard guard(c->device);
     cudaStreamSynchronize(c->side);
     ncclCommDestroy(c->comm);
-    for (auto* v : {&c->ev_arrived, &c->ev_free, &c->t_comm, &c->t_spmm})
+    for (auto* v : {&c->ev_arrived, &c->ev_free, &c->ev_packed, &c->t_comm, &c->t_spmm})
         for (cudaEvent_t e : *v) cudaEventDestroy(e);
     cudaEventDestroy(c->ev_input);
     cudaEventDestroy(c->t_begin);
@@ -334,6 +335,75 @@ extern "C" int dg_bcast_spmm_ordered(dg_comm* comm, dg_comm* row_comm, int32_t n
     if (timed) {
         DG_CUDA(cudaEventRecord(comm->t_end, compute));
         comm->timed_stages = n_products;
+    }
+    return DG_OK;
+}
+
+// 1D distributed product pipelined along the FEATURE dimension instead of along the source rank: the operand is cut
+// into column chunks; chunk c of every rank's block is all-gathered (one bandwidth-optimal collective) into a
+// (P*n) x w_c area while the compute stream multiplies chunk c-1 with the rank's whole n x (P*n) row block.  Every
+// product sees full-length rows (as on one GPU), z is written exactly once (no read-modify-write between stages), and
+// inside a row the sum runs over ascending (source rank, column) - the order of the reference's stage loop.
+extern "C" int dg_allgather_spmm(dg_comm* comm, const dg_plan* plan, const float* val, const float* x_local, int32_t n,
+                                 int32_t F, int32_t n_chunks, const int32_t* chunk_widths, float* const* pack,
+                                 float* const* area, float* z, int timed, void* compute_stream)
+{
+    cudaStream_t compute = (cudaStream_t)compute_stream;
+    if (!comm || !plan) return DG_ERR_NULL;
+    if (n < 0 || F < 0 || n_chunks < 1 || !chunk_widths) return DG_ERR_DIMS;
+    if (plan->m != n || (int64_t)plan->k != (int64_t)n * comm->nranks) return DG_ERR_DIMS;
+    int total = 0;
+    for (int c = 0; c < n_chunks; ++c) {
+        if (chunk_widths[c] <= 0) return DG_ERR_DIMS;
+        total += chunk_widths[c];
+    }
+    if (total != F) return DG_ERR_DIMS;
+    if ((int64_t)n * F == 0) return DG_OK;
+    if (!x_local || !z || !area || !area[0] || !area[1] || (n_chunks > 1 && (!pack || !pack[0] || !pack[1]))) return DG_ERR_NULL;
+    int rc;
+    DeviceGuard guard(comm->device);
+    if ((rc = make_events(comm->ev_arrived, 2, cudaEventDisableTiming))) return rc;
+    if ((rc = make_events(comm->ev_free, 2, cudaEventDisableTiming))) return rc;
+    if ((rc = make_events(comm->ev_packed, 2, cudaEventDisableTiming))) return rc;
+    comm->timed_stages = 0;
+    if (timed) {
+        if ((rc = make_events(comm->t_comm, 2 * (size_t)n_chunks, cudaEventDefault))) return rc;
+        if ((rc = make_events(comm->t_spmm, 2 * (size_t)n_chunks, cudaEventDefault))) return rc;
+        DG_CUDA(cudaEventRecord(comm->t_begin, compute));
+    }
+    auto stage_in = [&](int c, int c0) -> int {      // pack chunk c on the compute stream, gather it on the side stream
+        const int b = c & 1, w = chunk_widths[c];
+        const float* send = x_local;
+        if (n_chunks > 1) {
+            DG_CUDA(cudaMemcpy2DAsync(pack[b], (size_t)w * 4, x_local + c0, (size_t)F * 4, (size_t)w * 4, (size_t)n,
+                                      cudaMemcpyDeviceToDevice, compute));
+            send = pack[b];
+        }
+        DG_CUDA(cudaEventRecord(comm->ev_packed[b], compute));
+        DG_CUDA(cudaStreamWaitEvent(comm->side, comm->ev_packed[b], 0));
+        if (c >= 2) DG_CUDA(cudaStreamWaitEvent(comm->side, comm->ev_free[b], 0));
+        if (timed) DG_CUDA(cudaEventRecord(comm->t_comm[2 * c], comm->side));
+        DG_NCCL(ncclAllGather(send, area[b], (size_t)n * w, ncclFloat, comm->comm, comm->side));
+        if (timed) DG_CUDA(cudaEventRecord(comm->t_comm[2 * c + 1], comm->side));
+        DG_CUDA(cudaEventRecord(comm->ev_arrived[b], comm->side));
+        return DG_OK;
+    };
+    std::vector<int> first(n_chunks + 1, 0);
+    for (int c = 0; c < n_chunks; ++c) first[c + 1] = first[c] + chunk_widths[c];
+    if ((rc = stage_in(0, 0))) return rc;
+    for (int c = 0; c < n_chunks; ++c) {
+        const int b = c & 1, w = chunk_widths[c];
+        if (c + 1 < n_chunks && (rc = stage_in(c + 1, first[c + 1]))) return rc;   // next chunk travels during this product
+        DG_CUDA(cudaStreamWaitEvent(compute, comm->ev_arrived[b], 0));
+        if (timed) DG_CUDA(cudaEventRecord(comm->t_spmm[2 * c], compute));
+        rc = dg_spmm_csr(plan, val, area[b], w, z + first[c], F, w, 1.f, 0.f, 0u, nullptr, nullptr, compute);
+        if (rc) return rc;
+        if (timed) DG_CUDA(cudaEventRecord(comm->t_spmm[2 * c + 1], compute));
+        DG_CUDA(cudaEventRecord(comm->ev_free[b], compute));
+    }
+    if (timed) {
+        DG_CUDA(cudaEventRecord(comm->t_end, compute));
+        comm->timed_stages = n_chunks;
     }
     return DG_OK;
 }

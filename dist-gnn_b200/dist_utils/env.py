@@ -42,8 +42,10 @@ class DistEnv:
         # 'reference': products in ascending stage order (the reference's sum order), two receive buffers;
         # 'local_first': own block first, one receive area for all remote blocks, every broadcast queued up front
         self.stage_order = stage_order if stage_order is not None else os.environ.get('DIST_GNN_STAGE_ORDER', 'reference')
-        if self.stage_order not in ('reference', 'local_first'):
+        # 'feature_chunks' (1D): all-gather the operand one column chunk at a time, one full-row product per chunk
+        if self.stage_order not in ('reference', 'local_first', 'feature_chunks'):
             raise ValueError(f'unknown stage order {self.stage_order!r}')
+        self.chunk_width = int(os.environ.get('DIST_GNN_CHUNK_WIDTH', 64))
         DistEnv.env = self
 
     def __repr__(self):
@@ -119,13 +121,14 @@ class DistEnv:
     def stages(self):
         return schedule.stages(self.rank, self.world_size, self.rep)
 
-    def recv_buffers(self, n, F, nbuf=2):
-        """nbuf persistent receive buffers able to hold one n x F block, reused by every stage loop."""
+    def recv_buffers(self, n, F, nbuf=2, tag='recv'):
+        """nbuf persistent buffers able to hold an n x F block each, reused by every stage loop; `tag` keeps apart the
+        sets that are live at the same time (receive areas, pack buffers)."""
         need = n * F
-        bufs = self._recv.get(nbuf)
+        bufs = self._recv.get((tag, nbuf))
         if bufs is None or bufs[0].numel() < need:
             bufs = [torch.empty(need, dtype=torch.float32, device=self.device) for _ in range(nbuf)]
-            self._recv[nbuf] = bufs
+            self._recv[(tag, nbuf)] = bufs
         return [b[:need].view(n, F) for b in bufs]
 
     def shutdown(self):

@@ -68,6 +68,15 @@ def broadcast(local_adj_parts, local_feature, tag):
     stages = env.stages()
     comm = env.col_comm
     z = torch.empty_like(x)
+    if comm is not None and env.stage_order == 'feature_chunks' and env.rep == 1:
+        # 1D only: pipeline along the feature dimension (all-gather of column chunks, full-length rows per product)
+        plan = group_plans(local_adj_parts, [st.part for st in stages], len(stages))[0]
+        widths = spmm_cpp.chunk_widths(width, env.chunk_width)
+        pack = env.recv_buffers(n, max(widths), nbuf=2, tag='pack')
+        area = env.recv_buffers(n * comm.size, max(widths), nbuf=2, tag='area')
+        with env.timer.timing_cuda('broadcast+spmm'):
+            spmm_cpp.allgather_spmm(comm, plan, x, pack, area, z, widths)
+        return z
     if comm is not None and env.stage_order == 'local_first':
         with env.timer.timing_cuda('broadcast+spmm'):
             spmm_cpp.bcast_spmm_ordered(comm, *ordered_products(env, local_adj_parts, stages, x), x, z,

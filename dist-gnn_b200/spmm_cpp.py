@@ -70,6 +70,7 @@ def lib():
             'dg_bcast_spmm_1d': ([vp, i32, vp, i32, vp, vp, vp, i32, i32, vp, i32, vp, ctypes.c_int, vp], ctypes.c_int),
             'dg_bcast_spmm_15d': ([vp, vp, i32, vp, i32, vp, vp, vp, i32, i32, vp, i32, vp, ctypes.c_int, vp], ctypes.c_int),
             'dg_bcast_spmm_ordered': ([vp, vp, i32, vp, i32, vp, i32, vp, vp, vp, vp, vp, i32, i32, vp, ctypes.c_int, vp], ctypes.c_int),
+            'dg_allgather_spmm': ([vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp, ctypes.c_int, vp], ctypes.c_int),
             'dg_comm_last_times': ([vp, ctypes.POINTER(StageTimes)], ctypes.c_int),
             'dg_select_kernel': ([ctypes.c_int], ctypes.c_int),
             'dg_profile_begin': ([], ctypes.c_int),
@@ -330,4 +331,35 @@ def bcast_spmm_ordered(comm, roots, landing, products, x_local, z, row_comm=None
     with torch.cuda.device(x_local.device):
         check(lib().dg_bcast_spmm_ordered(comm.handle, row_comm.handle if row_comm else None, S, roots_arr, bcast_group, land_arr, P, plan_arr,
                                           val_arr, op_arr, last_arr, x_local.data_ptr(), n, F, z.data_ptr(), int(timed), _stream()))
+    return z
+
+
+def chunk_widths(F, target=64):
+    """Column chunks for allgather_spmm: widths that are multiples of 4 (16-byte aligned pieces) near `target`, last one
+    takes the rest.  Narrow or odd operands stay in one piece."""
+    if F < 2 * target or F % 4:
+        return [F]
+    widths = [target] * (F // target)
+    if F % target:
+        widths[-1] += F % target
+    return widths
+
+
+def allgather_spmm(comm, plan, x_local, pack, area, z, widths, timed=False):
+    """dg_allgather_spmm: z <- A_rowblock @ allgather(x) pipelined over column chunks of the given widths.
+
+    plan   SpmmPlan of the rank's whole n x (P*n) row block;  pack / area: two fp32 CUDA buffers each, of at least
+    n * max(widths) and P * n * max(widths) floats."""
+    _dev_tensor(x_local, torch.float32, 'x_local'), _dev_tensor(z, torch.float32, 'z')
+    n, F = x_local.shape
+    w_arr = (ctypes.c_int32 * len(widths))(*widths)
+    for t, need, what in ((pack[0], n, 'pack'), (pack[1], n, 'pack'), (area[0], n * comm.size, 'area'), (area[1], n * comm.size, 'area')):
+        _dev_tensor(t, torch.float32, what + ' buffer')
+        if t.numel() < need * max(widths):
+            raise RuntimeError(f'{what} buffer too small')
+    pack_arr = (ctypes.c_void_p * 2)(pack[0].data_ptr(), pack[1].data_ptr())
+    area_arr = (ctypes.c_void_p * 2)(area[0].data_ptr(), area[1].data_ptr())
+    with torch.cuda.device(x_local.device):
+        check(lib().dg_allgather_spmm(comm.handle, plan.handle, plan.values.data_ptr(), x_local.data_ptr(), n, F, len(widths), w_arr,
+                                      pack_arr, area_arr, z.data_ptr(), int(timed), _stream()))
     return z

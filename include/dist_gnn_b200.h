@@ -172,6 +172,17 @@ int dg_bcast_spmm_ordered(dg_comm* comm, dg_comm* row_comm, int32_t n_stages, co
                           const float* const* host_vals, const float* const* host_operands,
                           const int32_t* host_last_stage, const float* x_local, int32_t n, int32_t F, float* z,
                           int timed, void* compute_stream);
+/* 1D only: the same distributed product pipelined along the feature dimension (replaces gcn.py:16-30 as a whole).  The
+ * n x F operand is cut into n_chunks column chunks (host_chunk_widths, summing to F).  Chunk c of every rank is
+ * all-gathered on the side stream into host_area[c % 2] ((nranks*n) x w_c, rank r's rows at r*n) while the compute
+ * stream multiplies chunk c-1 by `plan`, the rank's whole n x (nranks*n) row block, writing columns of z directly
+ * (leading dimension F, beta = 0: z is written once).  Rows keep their full length, so the product runs as on one
+ * GPU, and the sum inside a row is over ascending (source rank, column) as in the reference's stage loop.
+ *   host_pack[0..2)   two buffers of n * max(w_c) floats for the packed chunk to send (unused when n_chunks == 1)
+ *   host_area[0..2)   two buffers of nranks * n * max(w_c) floats */
+int dg_allgather_spmm(dg_comm* comm, const dg_plan* plan, const float* val, const float* x_local, int32_t n, int32_t F,
+                      int32_t n_chunks, const int32_t* host_chunk_widths, float* const* host_pack,
+                      float* const* host_area, float* z, int timed, void* compute_stream);
 int dg_comm_last_times(dg_comm* comm, dg_stage_times* host_out);
 
 /* ---- instrumentation (no counterpart in the reference, whose timer synchronises the device around every call,
