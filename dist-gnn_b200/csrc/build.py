@@ -29,6 +29,7 @@ def command(verbose=False):
     cmd = ['nvcc', '-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-O3', '-std=c++17',
            '-Xcompiler', '-fPIC,-Wall', '-shared', '-I', os.path.join(ROOT, 'include'), '-I', inc,
            '-L', lib, '-l:libnccl.so.2', '-Xlinker', f'-rpath={lib}', '-o', OUTPUT] + srcs
+    cmd[1:1] = os.environ.get('DG_NVCC_EXTRA', '').split()      # e.g. -DDG_ROWS_MIN_BLOCKS=4 for tuning experiments
     if verbose:
         cmd.insert(1, '-Xptxas=-v')
     return cmd, srcs
