@@ -44,7 +44,7 @@ def parse():
     ap.add_argument('--stage-order', default=None, choices=['reference', 'local_first', 'feature_chunks'],
                     help='order of the products inside a distributed SpMM (default: that of DistEnv)')
     ap.add_argument('--chunk-width', type=int, default=0, help='column chunk width of the feature_chunks order (0 = default 64)')
-    ap.add_argument('--dense', default=None, choices=['fp32', '3xtf32'],
+    ap.add_argument('--dense', default=None, choices=['fp32', '3xtf32', 'tcgen05'],
                     help='dense transform: fp32 library GEMM, or three tensor-core TF32 passes with fp32 accumulation')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--profiler-range', action='store_true',

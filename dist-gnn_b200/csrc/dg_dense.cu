@@ -1,0 +1,349 @@
+// Dense transform of the GCN layer on the 5th-generation tensor cores:  C[M x N] = act(A[M x K] * Bt[N x K]^T), fp32 in
+// and out, for the tall-skinny shapes either side of the SpMM (Z*W and AG*W^T: light_dist_gnn/models/gcn.py:41, :49;
+// M = rows of the rank's block, K and N <= 256).
+//
+// fp32 accuracy from TF32 tensor cores: every operand is cut into a TF32-exact head (sign, exponent, top 10 mantissa
+// bits) and its residual tail, and the accumulator (fp32, in tensor memory) receives
+//     A_head*B_head + A_head*B_tail + A_tail*B_head
+// (the dropped tail*tail term is 2^-22 relative).  The small matrix Bt is split once on the host side of the call
+// (dg_dense_split); A is split inside the kernel, in shared memory, on its way from TMA to the MMA.
+//
+// One CTA computes a 128-row tile.  Warp 0 drives TMA (128B-swizzled boxes of 32 K-columns: A rows, Bt head, Bt tail)
+// through a 2-stage ring; warps 2-5 split A in place (head) and into a second buffer (tail), fence it to the async
+// proxy and later drain the accumulator (tcgen05.ld) to global memory with the optional ReLU; one thread of warp 1 issues
+// the tcgen05.mma instructions (kind::tf32, 128 x N x 8, operands described by shared-memory matrix descriptors,
+// accumulator in 256 TMEM columns) and commits them to the mbarriers that recycle the stages.
+// Every mbarrier wait is bounded; a role that gives up sets the status word and the CTA still frees its TMEM.
+#include <cuda.h>
+#include <cstdint>
+#include "dg_internal.h"
+
+namespace {
+
+constexpr int BM = 128;             // rows per CTA tile (UMMA M)
+constexpr int BK = 32;              // fp32 K-columns per stage = one 128-byte swizzle row
+constexpr int STAGES = 2;
+constexpr int kWaitLimit = 1 << 22;
+constexpr int kThreads = 192;
+
+struct DenseArgs {
+    float* C;
+    int64_t ldc;
+    int64_t M;
+    int32_t N, K, n_pad;            // n_pad = N rounded up to 16 (UMMA N)
+    uint32_t relu;
+    int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)      // bounded
+{
+    for (int i = 0; i < kWaitLimit; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+// Shared-memory matrix descriptor of a K-major tile stored as 128-byte rows with the 128B swizzle: 8-row groups are
+// 1024 bytes apart (stride byte offset), the leading byte offset is unused for this layout, descriptor version 1.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);            // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                                   // leading byte offset (ignored with swizzle), 16-byte units
+    d |= (uint64_t)(1024 >> 4) << 32;                         // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                                   // descriptor version for sm_100
+    d |= (uint64_t)2 << 61;                                   // layout type: SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor for kind::tf32: fp32 accumulator, TF32 A and B, both K-major, shape 128 x n_pad.
+__device__ __forceinline__ uint32_t umma_idesc_tf32(int n_pad)
+{
+    uint32_t d = 0;
+    d |= 1u << 4;                                             // accumulator format: F32
+    d |= 2u << 7;                                             // A format: TF32
+    d |= 2u << 10;                                            // B format: TF32
+    d |= (uint32_t)(n_pad >> 3) << 17;                        // N / 8
+    d |= (uint32_t)(BM >> 4) << 24;                           // M / 16
+    return d;
+}
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+}  // namespace
+
+namespace {
+
+__global__ void __launch_bounds__(kThreads, 1)
+k_dense_nt(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmBh,
+           const __grid_constant__ CUtensorMap tmBt, const DenseArgs a)
+{
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;                 // swizzled tiles need 1024-byte alignment
+    unsigned char* gbase = smem_raw + (base - raw);
+    const int b_bytes = a.n_pad * 128;                            // one slab of Bt: n_pad rows x 128 bytes
+    const int stage_bytes = 2 * BM * 128 + 2 * b_bytes;           // A head, A tail, Bt head, Bt tail
+    const uint32_t bars = base + STAGES * stage_bytes;
+    const uint32_t full0 = bars, ready0 = bars + 8 * STAGES, empty0 = bars + 16 * STAGES, acc_full = bars + 24 * STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + STAGES * stage_bytes + 24 * STAGES + 8);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t m0 = (int64_t)blockIdx.x * BM;
+    const int nslabs = (a.K + BK - 1) / BK;
+    int tmem_cols = 32;
+    while (tmem_cols < a.n_pad) tmem_cols <<= 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(ready0 + 8 * s, 128);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(acc_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {                                              // one warp allocates the accumulator columns
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {                                          // TMA producer
+            for (int i = 0; i < nslabs && ok; ++i) {
+                const int s = i % STAGES, u = i / STAGES;
+                if (u > 0) ok = mbar_wait(empty0 + 8 * s, (u - 1) & 1);
+                if (!ok) break;
+                const uint32_t st = base + s * stage_bytes;
+                mbar_expect_tx(full0 + 8 * s, BM * 128 + 2 * b_bytes);
+                tma_load_2d(st, &tmA, i * BK, (int)m0, full0 + 8 * s);
+                tma_load_2d(st + 2 * BM * 128, &tmBh, i * BK, 0, full0 + 8 * s);
+                tma_load_2d(st + 2 * BM * 128 + b_bytes, &tmBt, i * BK, 0, full0 + 8 * s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {                                          // MMA issuer
+            const uint32_t idesc = umma_idesc_tf32(a.n_pad);
+            for (int i = 0; i < nslabs && ok; ++i) {
+                const int s = i % STAGES, u = i / STAGES;
+                ok = mbar_wait(ready0 + 8 * s, u & 1);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t st = base + s * stage_bytes;
+                const uint64_t a_head = umma_desc_sw128(st), a_tail = umma_desc_sw128(st + BM * 128);
+                const uint64_t b_head = umma_desc_sw128(st + 2 * BM * 128), b_tail = umma_desc_sw128(st + 2 * BM * 128 + b_bytes);
+#pragma unroll
+                for (int k = 0; k < BK / 8; ++k) {               // 8 TF32 columns = 32 bytes per MMA: +2 in 16-byte units
+                    umma_tf32(tmem, a_tail + 2 * k, b_head + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    umma_tf32(tmem, a_head + 2 * k, b_tail + 2 * k, idesc, 1u);
+                    umma_tf32(tmem, a_head + 2 * k, b_head + 2 * k, idesc, 1u);
+                }
+                umma_commit(empty0 + 8 * s);                      // the stage is free once these MMAs have read it
+            }
+            if (ok) umma_commit(acc_full);
+        }
+    } else {
+        const int t = threadIdx.x - 64;                           // 0..127: split A, then drain the accumulator
+        for (int i = 0; i < nslabs && ok; ++i) {
+            const int s = i % STAGES, u = i / STAGES;
+            ok = mbar_wait(full0 + 8 * s, u & 1);
+            if (!ok) break;
+            float4* head = reinterpret_cast<float4*>(gbase + (size_t)s * stage_bytes);
+            float4* tail = head + BM * 128 / 16;
+#pragma unroll 4
+            for (int j = t; j < BM * 128 / 16; j += 128) {
+                const float4 x = head[j];
+                float4 h;
+                h.x = __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u); h.y = __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
+                h.z = __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u); h.w = __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
+                head[j] = h;
+                tail[j] = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(ready0 + 8 * s);
+        }
+        if (ok) ok = mbar_wait(acc_full, 0);
+        ok = __all_sync(0xffffffffu, ok);                         // tcgen05.ld below is warp-collective: decide as a warp
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int q = warp & 3;                               // a warp may only read its own quarter of the TMEM lanes
+            const int64_t row = m0 + q * 32 + lane;
+            float* crow = a.C + row * a.ldc;
+            const bool vec_ok = (a.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.C) & 15) == 0);
+            for (int c0 = 0; c0 < a.n_pad; c0 += 16) {
+                uint32_t r[16];
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                    : "r"(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row < a.M) {
+                    float v[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        v[j] = __uint_as_float(r[j]);
+                        if (a.relu) v[j] = fmaxf(v[j], 0.f);
+                    }
+                    if (vec_ok && c0 + 16 <= a.N) {
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(crow + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (c0 + j < a.N) crow[c0 + j] = v[j];
+                    }
+                }
+            }
+        }
+    }
+    if (!ok) atomicExch(a.status, 1);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
+}
+
+__global__ void k_tf32_split(const float* __restrict__ src, float* __restrict__ head, float* __restrict__ tail, int64_t count)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const float x = src[i];
+    const float h = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+    head[i] = h;
+    tail[i] = x - h;
+}
+
+}  // namespace
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled()
+{
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// 2-D fp32 row-major matrix [rows x cols] with leading dimension ld, boxes of 32 columns x box_rows rows, 128B swizzle,
+// out-of-range elements read as zero.
+int make_map(CUtensorMap* map, const float* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows)
+{
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return DG_ERR_UNSUPPORTED;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? DG_OK : DG_ERR_UNSUPPORTED;
+}
+
+int* dense_status_word()
+{
+    static int* word[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!word[dev]) {
+        if (cudaMalloc((void**)&word[dev], sizeof(int)) != cudaSuccess) return nullptr;
+        cudaMemset(word[dev], 0, sizeof(int));
+    }
+    return word[dev];
+}
+
+}  // namespace
+
+extern "C" int dg_dense_split(const float* src, float* head, float* tail, int64_t count, void* stream)
+{
+    if (count < 0) return DG_ERR_DIMS;
+    if (count == 0) return DG_OK;
+    if (!src || !head || !tail) return DG_ERR_NULL;
+    k_tf32_split<<<(unsigned)((count + 255) / 256), 256, 0, (cudaStream_t)stream>>>(src, head, tail, count);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int dg_dense_supported(int64_t M, int32_t N, int32_t K, int64_t lda, int64_t ldb, const void* A, const void* Bh, const void* Bt)
+{
+    if (M <= 0 || N <= 0 || K <= 0 || N > 256 || M >= ((int64_t)1 << 31)) return 0;
+    if (lda % 4 || ldb % 4 || lda < K || ldb < K) return 0;                       // TMA strides are multiples of 16 bytes
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(Bh) | reinterpret_cast<uintptr_t>(Bt)) & 15) return 0;
+    return encode_tiled() != nullptr;
+}
+
+extern "C" int dg_dense_nt(const float* A, int64_t lda, const float* Bt_head, const float* Bt_tail, int64_t ldb, float* C,
+                           int64_t ldc, int64_t M, int32_t N, int32_t K, int32_t relu, void* stream)
+{
+    if (!A || !Bt_head || !Bt_tail || !C) return DG_ERR_NULL;
+    if (ldc < N) return DG_ERR_DIMS;
+    if (!dg_dense_supported(M, N, K, lda, ldb, A, Bt_head, Bt_tail)) return DG_ERR_UNSUPPORTED;
+    DenseArgs a{};
+    a.C = C; a.ldc = ldc; a.M = M; a.N = N; a.K = K; a.n_pad = (N + 15) / 16 * 16; a.relu = relu ? 1u : 0u;
+    a.status = dense_status_word();
+    if (!a.status) return DG_ERR_STATE;
+    CUtensorMap tmA, tmBh, tmBt;
+    int rc;
+    if ((rc = make_map(&tmA, A, M, K, lda, BM)) || (rc = make_map(&tmBh, Bt_head, N, K, ldb, a.n_pad)) ||
+        (rc = make_map(&tmBt, Bt_tail, N, K, ldb, a.n_pad)))
+        return rc;
+    const size_t smem = (size_t)STAGES * (2 * BM * 128 + 2 * a.n_pad * 128) + 24 * STAGES + 16 + 1024;
+    DG_CUDA(cudaFuncSetAttribute(k_dense_nt, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    k_dense_nt<<<(unsigned)((M + BM - 1) / BM), kThreads, smem, (cudaStream_t)stream>>>(tmA, tmBh, tmBt, a);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int dg_dense_status(int* host_status, void* stream)
+{
+    if (!host_status) return DG_ERR_NULL;
+    int* w = dense_status_word();
+    if (!w) return DG_ERR_STATE;
+    DG_CUDA(cudaMemcpyAsync(host_status, w, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    DG_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return DG_OK;
+}

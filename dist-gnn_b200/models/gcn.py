@@ -27,6 +27,9 @@ def spmm(A, B, C):
 
 # How the dense transforms around the SpMM (torch.mm at gcn.py:41, :49-50) are computed:
 #   'fp32'    plain fp32 library GEMM (CUDA cores), bit-for-bit what the reference's torch.mm does on a GPU
+#   'tcgen05' the library's own tensor-core kernel (dg_dense_nt): three TF32 passes on head/tail splits, fp32 accumulator
+#             in tensor memory, the split of the tall operand done inside the kernel; covers Z*W and AG*W^T, the
+#             weight-gradient product X^T*AG stays on the fp32 library GEMM
 #   '3xtf32'  each fp32 operand is cut into a TF32-exact head and its residual, and the product is accumulated in fp32
 #             from three tensor-core TF32 GEMMs  head*head + head*tail + tail*head  (the tail*tail term, 2^-22 relative,
 #             is dropped).  About 5e-7 relative error per product - inside the 1e-5 parity bound - at a fraction of the
@@ -41,6 +44,11 @@ def _tf32_split(x):
 
 def dense_mm(a, b, ta=False, tb=False):
     """op(a) @ op(b) for fp32 CUDA matrices according to DENSE_MODE; ta / tb transpose the (contiguous) operand."""
+    if DENSE_MODE == 'tcgen05' and a.is_cuda and not ta:
+        # hand-written tensor-core kernel: a [M x K] times a small matrix given as bt [N x K]; other shapes fall through
+        out = spmm_cpp.dense_nt(a.contiguous(), b.contiguous() if tb else b.t().contiguous())
+        if out is not None:
+            return out
     if DENSE_MODE != '3xtf32' or not a.is_cuda:
         return torch.mm(a.t() if ta else a, b.t() if tb else b)
     (ah, at), (bh, bt) = _tf32_split(a), _tf32_split(b)

@@ -73,6 +73,10 @@ def lib():
             'dg_allgather_spmm': ([vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp, ctypes.c_int, vp], ctypes.c_int),
             'dg_comm_last_times': ([vp, ctypes.POINTER(StageTimes)], ctypes.c_int),
             'dg_select_kernel': ([ctypes.c_int], ctypes.c_int),
+            'dg_dense_split': ([vp, vp, vp, i64, vp], ctypes.c_int),
+            'dg_dense_supported': ([i64, i32, i32, i64, i64, vp, vp, vp], ctypes.c_int),
+            'dg_dense_nt': ([vp, i64, vp, vp, i64, vp, i64, i64, i32, i32, i32, vp], ctypes.c_int),
+            'dg_dense_status': ([ctypes.POINTER(ctypes.c_int), vp], ctypes.c_int),
             'dg_profile_begin': ([], ctypes.c_int),
             'dg_profile_end': ([ctypes.POINTER(Profile)], ctypes.c_int),
         }
@@ -363,3 +367,36 @@ def allgather_spmm(comm, plan, x_local, pack, area, z, widths, timed=False):
         check(lib().dg_allgather_spmm(comm.handle, plan.handle, plan.values.data_ptr(), x_local.data_ptr(), n, F, len(widths), w_arr,
                                       pack_arr, area_arr, z.data_ptr(), int(timed), _stream()))
     return z
+
+
+def dense_split(w):
+    """TF32-exact head and residual tail of a small fp32 CUDA matrix (dg_dense_split); head + tail == w exactly."""
+    _dev_tensor(w, torch.float32, 'matrix')
+    head, tail = torch.empty_like(w), torch.empty_like(w)
+    with torch.cuda.device(w.device):
+        check(lib().dg_dense_split(w.data_ptr(), head.data_ptr(), tail.data_ptr(), w.numel(), _stream()))
+    return head, tail
+
+
+def dense_nt(a, bt, relu=False):
+    """a [M x K] @ bt[N x K]^T on the tensor cores with fp32 accuracy (dg_dense_nt), or None when the shapes or strides
+    are outside what the kernel takes (the caller then uses a library GEMM)."""
+    _dev_tensor(a, torch.float32, 'a'), _dev_tensor(bt, torch.float32, 'bt')
+    M, K = a.shape
+    N = bt.size(0)
+    if bt.size(1) != K:
+        raise RuntimeError(f'inner dimensions differ: {tuple(a.shape)} x {tuple(bt.shape)}^T')
+    if M == 0 or not lib().dg_dense_supported(M, N, K, K, K, a.data_ptr(), bt.data_ptr(), bt.data_ptr()):
+        return None
+    head, tail = dense_split(bt)
+    c = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    with torch.cuda.device(a.device):
+        check(lib().dg_dense_nt(a.data_ptr(), K, head.data_ptr(), tail.data_ptr(), K, c.data_ptr(), N, M, N, K, int(relu), _stream()))
+    return c
+
+
+def dense_status():
+    """0, or non-zero if a dense-transform kernel gave up on one of its bounded waits since the process started."""
+    out = ctypes.c_int(-1)
+    check(lib().dg_dense_status(ctypes.byref(out), _stream()))
+    return out.value

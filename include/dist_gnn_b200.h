@@ -185,6 +185,20 @@ int dg_allgather_spmm(dg_comm* comm, const dg_plan* plan, const float* val, cons
                       float* const* host_area, float* z, int timed, void* compute_stream);
 int dg_comm_last_times(dg_comm* comm, dg_stage_times* host_out);
 
+/* ---- dense transform on the tensor cores ----------------------------------------------------------------------------
+ * C[M x N] = act(A[M x K] * Bt[N x K]^T), fp32 in and out, replacing torch.mm at models/gcn.py:41 (Bt = W^T) and :49
+ * (Bt = W).  Three tcgen05 TF32 passes on head/tail splits with an fp32 accumulator in tensor memory give fp32-level
+ * accuracy (about 5e-7 relative).  Bt is passed already split (dg_dense_split: head keeps sign, exponent and 10 mantissa
+ * bits, tail = x - head); A is split inside the kernel.  Limits (dg_dense_supported returns 0 otherwise, and
+ * dg_dense_nt DG_ERR_UNSUPPORTED): N <= 256, M < 2^31, lda and ldb multiples of 4 floats, A / Bt 16-byte aligned.
+ * relu != 0 applies max(x, 0) on the way out.  dg_dense_status reads the device status word (synchronises `stream`):
+ * non-zero if a kernel gave up on one of its bounded waits (its output is then invalid; nothing hangs). */
+int dg_dense_split(const float* src, float* head, float* tail, int64_t count, void* stream);
+int dg_dense_supported(int64_t M, int32_t N, int32_t K, int64_t lda, int64_t ldb, const void* A, const void* Bt_head, const void* Bt_tail);
+int dg_dense_nt(const float* A, int64_t lda, const float* Bt_head, const float* Bt_tail, int64_t ldb, float* C, int64_t ldc,
+                int64_t M, int32_t N, int32_t K, int32_t relu, void* stream);
+int dg_dense_status(int* host_status, void* stream);
+
 /* ---- instrumentation (no counterpart in the reference, whose timer synchronises the device around every call,
  * light_dist_gnn/dist_utils/timer.py:16-24) ------------------------------------------------------------------------
  * Between dg_profile_begin and dg_profile_end every local product is bracketed by a CUDA event pair on the stream it

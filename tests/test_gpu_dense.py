@@ -1,0 +1,35 @@
+"""The tcgen05 dense transform (three TF32 passes, fp32 accumulation in tensor memory) against float64.  Needs a GPU."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-5
+
+
+@pytest.mark.parametrize('M,K,N', [(128, 32, 16), (128, 256, 256), (1000, 256, 256), (300, 100, 256), (129, 256, 47),
+                                   (5000, 32, 16), (77, 8, 8), (4096, 256, 128), (513, 100, 47)])
+def test_dense_nt_matches_float64(M, K, N):
+    import spmm_cpp
+    g = torch.Generator(device='cuda').manual_seed(M + K + N)
+    a = torch.randn(M, K, device='cuda', generator=g)
+    bt = torch.randn(N, K, device='cuda', generator=g)
+    c = spmm_cpp.dense_nt(a, bt)
+    assert c is not None and c.shape == (M, N)
+    want = a.double() @ bt.double().t()
+    assert_close(c.cpu().numpy(), want.cpu().numpy(), TOL, f'{M}x{K}x{N}')
+    r = spmm_cpp.dense_nt(a, bt, relu=True)
+    assert_close(r.cpu().numpy(), want.clamp(min=0).cpu().numpy(), TOL, f'relu {M}x{K}x{N}')
+    assert spmm_cpp.dense_status() == 0
+
+
+def test_dense_split_is_exact_and_unsupported_shapes_fall_back():
+    import spmm_cpp
+    w = torch.randn(64, 48, device='cuda')
+    head, tail = spmm_cpp.dense_split(w)
+    assert torch.equal(head + tail, w)
+    assert torch.equal(head.view(torch.int32) & 8191, torch.zeros_like(head, dtype=torch.int32))
+    assert spmm_cpp.dense_nt(torch.randn(100, 47, device='cuda'), torch.randn(16, 47, device='cuda')) is None     # 188-byte rows
+    assert spmm_cpp.dense_nt(torch.randn(100, 64, device='cuda'), torch.randn(300, 64, device='cuda')) is None     # N > 256
