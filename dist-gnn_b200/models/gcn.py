@@ -34,7 +34,7 @@ def spmm(A, B, C):
 #             from three tensor-core TF32 GEMMs  head*head + head*tail + tail*head  (the tail*tail term, 2^-22 relative,
 #             is dropped).  About 5e-7 relative error per product - inside the 1e-5 parity bound - at a fraction of the
 #             CUDA-core time, because these skinny GEMMs are then bound by reading the activations.
-DENSE_MODE = os.environ.get('DIST_GNN_DENSE', 'fp32')
+DENSE_MODE = os.environ.get('DIST_GNN_DENSE', 'tcgen05')
 
 
 def _tf32_split(x):
