@@ -347,3 +347,241 @@ extern "C" int dg_dense_status(int* host_status, void* stream)
     DG_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     return DG_OK;
 }
+
+// ---- weight-gradient product  D[Km x Nn] = X[n x Km]^T * G[n x Nn]  (models/gcn.py:50) -------------------------------------
+// The reduction runs over the n rows of the block, so both operands are read "MN-major": a TMA box of 32 columns x 16
+// rows lands as 16 rows of 128 bytes in the 32-byte-atom variant of the 128B swizzle, which is the one layout the tensor
+// cores accept for 32-bit MN-major operands (the plain 128B swizzle makes them read zeros); the boxes of one operand lie
+// 2048 bytes apart (leading byte offset), 4-row groups 512 bytes.  Each CTA streams a contiguous range
+// of rows through a 3-stage ring, splits BOTH operands into TF32 head and tail in shared memory, accumulates the three
+// passes into one or two 128 x Nn fp32 accumulators in tensor memory, and writes its partial D to scratch; a second
+// kernel adds the partials of all CTAs in CTA order (deterministic).
+namespace {
+
+constexpr int TN_ROWS = 16;                     // rows of X / G per stage (two MMA k-steps of 8)
+constexpr int TN_STAGES = 3;
+constexpr int TN_BOX_BYTES = TN_ROWS * 128;     // one 32-column box
+
+struct DenseTnArgs {
+    float* partial;                             // [gridDim.x][Km][Nn]
+    int64_t n;                                  // rows to reduce over
+    int64_t rows_per_cta;                       // multiple of TN_ROWS
+    int32_t Km, Nn, n_pad, m_halves;            // n_pad: Nn rounded up to 16; m_halves: 1 (Km <= 128) or 2
+    int* status;
+};
+
+// MN-major tile of 32-bit elements.  The tensor cores read such operands only in the "128B swizzle with 32-byte atoms"
+// layout (32-byte chunks of a 128-byte row XOR-ed with the row index modulo 4), which TMA writes in its
+// SWIZZLE_128B_ATOM_32B mode: 4-row groups are 512 bytes apart (stride byte offset), the 32-column boxes 2048 bytes
+// (leading byte offset).
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)(TN_BOX_BYTES >> 4) << 16;                 // leading byte offset: next 32 columns of M / N
+    d |= (uint64_t)(512 >> 4) << 32;                          // stride byte offset: next 4 rows of K
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)1 << 61;                                   // layout type: SWIZZLE_128B_BASE32B
+    return d;
+}
+__device__ __forceinline__ uint32_t umma_idesc_tf32_mn(int n_pad)
+{
+    return umma_idesc_tf32(n_pad) | (1u << 15) | (1u << 16);  // A and B are MN-major
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+k_dense_tn(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmG, const DenseTnArgs a)
+{
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    unsigned char* gbase = smem_raw + (base - raw);
+    const int x_boxes = a.m_halves * 4;                           // 32-column boxes covering the (padded) Km
+    const int g_boxes = (a.n_pad + 31) / 32;
+    const int x_bytes = x_boxes * TN_BOX_BYTES, g_bytes = g_boxes * TN_BOX_BYTES;
+    const int stage_bytes = 2 * x_bytes + 2 * g_bytes;            // X head, X tail, G head, G tail
+    const uint32_t bars = base + TN_STAGES * stage_bytes;
+    const uint32_t full0 = bars, ready0 = bars + 8 * TN_STAGES, empty0 = bars + 16 * TN_STAGES, acc_full = bars + 24 * TN_STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + TN_STAGES * stage_bytes + 24 * TN_STAGES + 8);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t r_begin = (int64_t)blockIdx.x * a.rows_per_cta;
+    const int64_t r_end = min(r_begin + a.rows_per_cta, a.n);
+    const int nslabs = r_end > r_begin ? (int)((r_end - r_begin + TN_ROWS - 1) / TN_ROWS) : 0;
+    int tmem_cols = 32;
+    while (tmem_cols < (a.m_halves == 2 ? 256 + a.n_pad : a.n_pad)) tmem_cols <<= 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TN_STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(ready0 + 8 * s, 128);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(acc_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {                                          // TMA producer
+            for (int i = 0; i < nslabs && ok; ++i) {
+                const int s = i % TN_STAGES, u = i / TN_STAGES;
+                if (u > 0) ok = mbar_wait(empty0 + 8 * s, (u - 1) & 1);
+                if (!ok) break;
+                const uint32_t st = base + s * stage_bytes;
+                const int r0 = (int)(r_begin + (int64_t)i * TN_ROWS);
+                mbar_expect_tx(full0 + 8 * s, x_bytes + g_bytes);
+                for (int j = 0; j < x_boxes; ++j) tma_load_2d(st + j * TN_BOX_BYTES, &tmX, 32 * j, r0, full0 + 8 * s);
+                for (int j = 0; j < g_boxes; ++j) tma_load_2d(st + 2 * x_bytes + j * TN_BOX_BYTES, &tmG, 32 * j, r0, full0 + 8 * s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {                                          // MMA issuer
+            const uint32_t idesc = umma_idesc_tf32_mn(a.n_pad);
+            for (int i = 0; i < nslabs && ok; ++i) {
+                const int s = i % TN_STAGES, u = i / TN_STAGES;
+                ok = mbar_wait(ready0 + 8 * s, u & 1);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t st = base + s * stage_bytes;
+                const uint64_t g_head = umma_desc_mn_sw128(st + 2 * x_bytes), g_tail = umma_desc_mn_sw128(st + 2 * x_bytes + g_bytes);
+                for (int h = 0; h < a.m_halves; ++h) {
+                    const uint64_t x_head = umma_desc_mn_sw128(st + h * 4 * TN_BOX_BYTES);
+                    const uint64_t x_tail = umma_desc_mn_sw128(st + x_bytes + h * 4 * TN_BOX_BYTES);
+                    const uint32_t acc = tmem + (uint32_t)(h * 256);
+#pragma unroll
+                    for (int k = 0; k < TN_ROWS / 8; ++k) {       // one 8-row group (1024 bytes) per MMA
+                        const uint64_t adv = (uint64_t)(k * (1024 >> 4));
+                        umma_tf32(acc, x_tail + adv, g_head + adv, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                        umma_tf32(acc, x_head + adv, g_tail + adv, idesc, 1u);
+                        umma_tf32(acc, x_head + adv, g_head + adv, idesc, 1u);
+                    }
+                }
+                umma_commit(empty0 + 8 * s);
+            }
+            if (ok) umma_commit(acc_full);
+        }
+    } else {
+        const int t = threadIdx.x - 64;
+        for (int i = 0; i < nslabs && ok; ++i) {
+            const int s = i % TN_STAGES, u = i / TN_STAGES;
+            ok = mbar_wait(full0 + 8 * s, u & 1);
+            if (!ok) break;
+            unsigned char* st = gbase + (size_t)s * stage_bytes;
+            for (int part = 0; part < 2; ++part) {                // X then G: head in place, tail behind it
+                float4* head = reinterpret_cast<float4*>(st + (part ? 2 * x_bytes : 0));
+                const int count = (part ? g_bytes : x_bytes) / 16;
+                float4* tail = head + count;
+                for (int j = t; j < count; j += 128) {
+                    const float4 x = head[j];
+                    float4 h;
+                    h.x = __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u); h.y = __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
+                    h.z = __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u); h.w = __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
+                    head[j] = h;
+                    tail[j] = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(ready0 + 8 * s);
+        }
+        if (ok && nslabs > 0) ok = mbar_wait(acc_full, 0);
+        ok = __all_sync(0xffffffffu, ok);
+        const int q = warp & 3;
+        float* out = a.partial + (size_t)blockIdx.x * a.Km * a.Nn;
+        for (int h = 0; h < a.m_halves; ++h) {
+            const int row = h * 128 + q * 32 + lane;              // row of D = column of X
+            for (int c0 = 0; c0 < a.n_pad; c0 += 16) {
+                uint32_t r[16];
+                if (ok && nslabs > 0) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                        : "r"(tmem + (uint32_t)(h * 256) + ((uint32_t)(q * 32) << 16) + (uint32_t)c0));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[j] = 0u;       // a CTA without rows contributes zeros
+                }
+                if (row < a.Km) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (c0 + j < a.Nn) out[(size_t)row * a.Nn + c0 + j] = __uint_as_float(r[j]);
+                }
+            }
+        }
+    }
+    if (!ok) atomicExch(a.status, 1);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
+}
+
+__global__ void k_dense_tn_reduce(const float* __restrict__ partial, int n_parts, int64_t elems, float* __restrict__ D, int64_t ldd, int32_t Nn)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= elems) return;
+    float sum = 0.f;
+    for (int p = 0; p < n_parts; ++p) sum += partial[(size_t)p * elems + i];
+    D[(i / Nn) * ldd + (i % Nn)] = sum;
+}
+
+int make_map_box(CUtensorMap* map, const float* ptr, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows)
+{
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return DG_ERR_UNSUPPORTED;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? DG_OK : DG_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+
+extern "C" int dg_dense_tn_supported(int64_t n, int32_t Km, int32_t Nn, int64_t ldx, int64_t ldg, const void* X, const void* G)
+{
+    if (n <= 0 || Km <= 0 || Nn <= 0 || Km > 256 || Nn > 256 || n >= ((int64_t)1 << 31)) return 0;
+    if (ldx % 4 || ldg % 4 || ldx < Km || ldg < Nn) return 0;
+    if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(G)) & 15) return 0;
+    return encode_tiled() != nullptr;
+}
+
+extern "C" int dg_dense_tn(const float* X, int64_t ldx, const float* G, int64_t ldg, float* D, int64_t ldd, int64_t n,
+                           int32_t Km, int32_t Nn, float* scratch, int64_t scratch_floats, int32_t max_ctas, void* stream)
+{
+    if (!X || !G || !D || !scratch) return DG_ERR_NULL;
+    if (ldd < Nn || max_ctas < 1) return DG_ERR_DIMS;
+    if (!dg_dense_tn_supported(n, Km, Nn, ldx, ldg, X, G)) return DG_ERR_UNSUPPORTED;
+    DenseTnArgs a{};
+    a.n = n; a.Km = Km; a.Nn = Nn; a.n_pad = (Nn + 15) / 16 * 16; a.m_halves = Km > 128 ? 2 : 1;
+    const int64_t slabs = (n + TN_ROWS - 1) / TN_ROWS;
+    const int ctas = (int)std::min<int64_t>(max_ctas, slabs);
+    a.rows_per_cta = (slabs + ctas - 1) / ctas * TN_ROWS;
+    if ((int64_t)ctas * Km * Nn > scratch_floats) return DG_ERR_SCRATCH;
+    a.partial = scratch;
+    a.status = dense_status_word();
+    if (!a.status) return DG_ERR_STATE;
+    CUtensorMap tmX, tmG;
+    int rc;
+    if ((rc = make_map_box(&tmX, X, n, Km, ldx, 32, TN_ROWS)) || (rc = make_map_box(&tmG, G, n, Nn, ldg, 32, TN_ROWS))) return rc;
+    const int x_bytes = a.m_halves * 4 * TN_BOX_BYTES, g_bytes = (a.n_pad + 31) / 32 * TN_BOX_BYTES;
+    const size_t smem = (size_t)TN_STAGES * (2 * x_bytes + 2 * g_bytes) + 24 * TN_STAGES + 16 + 1024;
+    DG_CUDA(cudaFuncSetAttribute(k_dense_tn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    k_dense_tn<<<ctas, kThreads, smem, (cudaStream_t)stream>>>(tmX, tmG, a);
+    const int64_t elems = (int64_t)Km * Nn;
+    k_dense_tn_reduce<<<(unsigned)((elems + 255) / 256), 256, 0, (cudaStream_t)stream>>>(scratch, ctas, elems, D, ldd, Nn);
+    return (int)cudaGetLastError();
+}

@@ -28,8 +28,8 @@ def spmm(A, B, C):
 # How the dense transforms around the SpMM (torch.mm at gcn.py:41, :49-50) are computed:
 #   'fp32'    plain fp32 library GEMM (CUDA cores), bit-for-bit what the reference's torch.mm does on a GPU
 #   'tcgen05' the library's own tensor-core kernel (dg_dense_nt): three TF32 passes on head/tail splits, fp32 accumulator
-#             in tensor memory, the split of the tall operand done inside the kernel; covers Z*W and AG*W^T, the
-#             weight-gradient product X^T*AG stays on the fp32 library GEMM
+#             in tensor memory, the tall operands split inside the kernel (dg_dense_nt for Z*W and AG*W^T, dg_dense_tn
+#             for the weight gradient X^T*AG); shapes it does not take (odd row strides such as 47) use the library GEMM
 #   '3xtf32'  each fp32 operand is cut into a TF32-exact head and its residual, and the product is accumulated in fp32
 #             from three tensor-core TF32 GEMMs  head*head + head*tail + tail*head  (the tail*tail term, 2^-22 relative,
 #             is dropped).  About 5e-7 relative error per product - inside the 1e-5 parity bound - at a fraction of the
@@ -47,6 +47,10 @@ def dense_mm(a, b, ta=False, tb=False):
     if DENSE_MODE == 'tcgen05' and a.is_cuda and not ta:
         # hand-written tensor-core kernel: a [M x K] times a small matrix given as bt [N x K]; other shapes fall through
         out = spmm_cpp.dense_nt(a.contiguous(), b.contiguous() if tb else b.t().contiguous())
+        if out is not None:
+            return out
+    if DENSE_MODE == 'tcgen05' and a.is_cuda and ta and not tb:
+        out = spmm_cpp.dense_tn(a.contiguous(), b.contiguous())      # a^T @ b with the reduction over the shared rows
         if out is not None:
             return out
     if DENSE_MODE != '3xtf32' or not a.is_cuda:

@@ -76,6 +76,8 @@ def lib():
             'dg_dense_split': ([vp, vp, vp, i64, vp], ctypes.c_int),
             'dg_dense_supported': ([i64, i32, i32, i64, i64, vp, vp, vp], ctypes.c_int),
             'dg_dense_nt': ([vp, i64, vp, vp, i64, vp, i64, i64, i32, i32, i32, vp], ctypes.c_int),
+            'dg_dense_tn_supported': ([i64, i32, i32, i64, i64, vp, vp], ctypes.c_int),
+            'dg_dense_tn': ([vp, i64, vp, i64, vp, i64, i64, i32, i32, vp, i64, i32, vp], ctypes.c_int),
             'dg_dense_status': ([ctypes.POINTER(ctypes.c_int), vp], ctypes.c_int),
             'dg_profile_begin': ([], ctypes.c_int),
             'dg_profile_end': ([ctypes.POINTER(Profile)], ctypes.c_int),
@@ -393,6 +395,30 @@ def dense_nt(a, bt, relu=False):
     with torch.cuda.device(a.device):
         check(lib().dg_dense_nt(a.data_ptr(), K, head.data_ptr(), tail.data_ptr(), K, c.data_ptr(), N, M, N, K, int(relu), _stream()))
     return c
+
+
+_tn_scratch = {}
+
+
+def dense_tn(x, g):
+    """x[n x Km]^T @ g[n x Nn] on the tensor cores with fp32 accuracy (dg_dense_tn), or None when the shapes or strides
+    are outside what the kernel takes.  Both operands are streamed once; per-CTA partial results are added in CTA order."""
+    _dev_tensor(x, torch.float32, 'x'), _dev_tensor(g, torch.float32, 'g')
+    n, Km = x.shape
+    Nn = g.size(1)
+    if g.size(0) != n:
+        raise RuntimeError(f'row counts differ: {tuple(x.shape)} vs {tuple(g.shape)}')
+    if n == 0 or not lib().dg_dense_tn_supported(n, Km, Nn, Km, Nn, x.data_ptr(), g.data_ptr()):
+        return None
+    ctas = torch.cuda.get_device_properties(x.device).multi_processor_count
+    scratch = _tn_scratch.get(x.device)
+    if scratch is None:
+        scratch = _tn_scratch[x.device] = torch.empty(ctas * 256 * 256, dtype=torch.float32, device=x.device)
+    d = torch.empty((Km, Nn), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().dg_dense_tn(x.data_ptr(), Km, g.data_ptr(), Nn, d.data_ptr(), Nn, n, Km, Nn, scratch.data_ptr(), scratch.numel(),
+                                ctas, _stream()))
+    return d
 
 
 def dense_status():

@@ -197,6 +197,14 @@ int dg_dense_split(const float* src, float* head, float* tail, int64_t count, vo
 int dg_dense_supported(int64_t M, int32_t N, int32_t K, int64_t lda, int64_t ldb, const void* A, const void* Bt_head, const void* Bt_tail);
 int dg_dense_nt(const float* A, int64_t lda, const float* Bt_head, const float* Bt_tail, int64_t ldb, float* C, int64_t ldc,
                 int64_t M, int32_t N, int32_t K, int32_t relu, void* stream);
+/* Weight-gradient product D[Km x Nn] = X[n x Km]^T * G[n x Nn] (torch.mm at models/gcn.py:50), same arithmetic (three
+ * TF32 passes, fp32 accumulator in tensor memory) with BOTH operands split inside the kernel.  The n rows are shared
+ * out over at most max_ctas CTAs; every CTA leaves a partial Km x Nn result in `scratch` (needs ctas * Km * Nn floats,
+ * DG_ERR_SCRATCH otherwise) and a second kernel adds the partials in CTA order, so the result is bit-reproducible.
+ * Limits: Km, Nn <= 256, n < 2^31, ldx and ldg multiples of 4 floats, X / G 16-byte aligned. */
+int dg_dense_tn_supported(int64_t n, int32_t Km, int32_t Nn, int64_t ldx, int64_t ldg, const void* X, const void* G);
+int dg_dense_tn(const float* X, int64_t ldx, const float* G, int64_t ldg, float* D, int64_t ldd, int64_t n, int32_t Km,
+                int32_t Nn, float* scratch, int64_t scratch_floats, int32_t max_ctas, void* stream);
 int dg_dense_status(int* host_status, void* stream);
 
 /* ---- instrumentation (no counterpart in the reference, whose timer synchronises the device around every call,

@@ -33,3 +33,24 @@ def test_dense_split_is_exact_and_unsupported_shapes_fall_back():
     assert torch.equal(head.view(torch.int32) & 8191, torch.zeros_like(head, dtype=torch.int32))
     assert spmm_cpp.dense_nt(torch.randn(100, 47, device='cuda'), torch.randn(16, 47, device='cuda')) is None     # 188-byte rows
     assert spmm_cpp.dense_nt(torch.randn(100, 64, device='cuda'), torch.randn(300, 64, device='cuda')) is None     # N > 256
+
+
+@pytest.mark.parametrize('n,Km,Nn', [(16, 32, 16), (1000, 256, 256), (5000, 100, 256), (300, 128, 48), (70000, 256, 256),
+                                     (33, 8, 8), (4099, 100, 64), (250000, 256, 128)])
+def test_dense_tn_matches_float64(n, Km, Nn):
+    import spmm_cpp
+    g = torch.Generator(device='cuda').manual_seed(n + Km + Nn)
+    x = torch.randn(n, Km, device='cuda', generator=g)
+    y = torch.randn(n, Nn, device='cuda', generator=g)
+    d = spmm_cpp.dense_tn(x, y)
+    assert d is not None and d.shape == (Km, Nn)
+    want = x.double().t() @ y.double()
+    assert_close(d.cpu().numpy(), want.cpu().numpy(), TOL, f'{n}x{Km}x{Nn}')
+    assert torch.equal(d, spmm_cpp.dense_tn(x, y))                 # partials are added in a fixed order
+    assert spmm_cpp.dense_status() == 0
+
+
+def test_dense_tn_unsupported_shapes_fall_back():
+    import spmm_cpp
+    assert spmm_cpp.dense_tn(torch.randn(100, 47, device='cuda'), torch.randn(100, 16, device='cuda')) is None
+    assert spmm_cpp.dense_tn(torch.randn(100, 64, device='cuda'), torch.randn(100, 300, device='cuda')) is None
