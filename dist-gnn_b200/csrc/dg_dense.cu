@@ -97,6 +97,15 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t a_desc, uint
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// 16 consecutive accumulator columns of this warp's 32 tensor-memory lanes (no wait: pair with tcgen05.wait::ld).
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -363,12 +372,20 @@ constexpr int TN_STAGES = 3;
 constexpr int TN_BOX_BYTES = TN_ROWS * 128;     // one 32-column box
 
 struct DenseTnArgs {
-    float* partial;                             // [gridDim.x][Km][Nn]
+    float* partial;                             // [gridDim.x][m_halves][n_pad / 16][4][128][4], see tn_partial_index
     int64_t n;                                  // rows to reduce over
     int64_t rows_per_cta;                       // multiple of TN_ROWS
     int32_t Km, Nn, n_pad, m_halves;            // n_pad: Nn rounded up to 16; m_halves: 1 (Km <= 128) or 2
+    int32_t flush_slabs;                        // slabs accumulated in tensor memory between two flushes
     int* status;
 };
+
+// Where element (m, c) of a CTA's partial D lives: the 128 rows of an accumulator half are the fastest index above a
+// float4 of columns, so that a warp that holds 32 rows of tensor memory moves 512 contiguous bytes per access.
+__host__ __device__ __forceinline__ int64_t tn_partial_index(int m, int c, int n_pad)
+{
+    return ((((int64_t)(m >> 7) * (n_pad >> 4) + (c >> 4)) * 4 + ((c & 15) >> 2)) * 128 + (m & 127)) * 4 + (c & 3);
+}
 
 // MN-major tile of 32-bit elements.  The tensor cores read such operands only in the "128B swizzle with 32-byte atoms"
 // layout (32-byte chunks of a 128-byte row XOR-ed with the row index modulo 4), which TMA writes in its
@@ -402,7 +419,9 @@ k_dense_tn(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUte
     const int stage_bytes = 2 * x_bytes + 2 * g_bytes;            // X head, X tail, G head, G tail
     const uint32_t bars = base + TN_STAGES * stage_bytes;
     const uint32_t full0 = bars, ready0 = bars + 8 * TN_STAGES, empty0 = bars + 16 * TN_STAGES, acc_full = bars + 24 * TN_STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + TN_STAGES * stage_bytes + 24 * TN_STAGES + 8);
+    const uint32_t acc_empty = acc_full + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + TN_STAGES * stage_bytes + 24 * TN_STAGES + 16);
+    const int T = a.flush_slabs;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t r_begin = (int64_t)blockIdx.x * a.rows_per_cta;
     const int64_t r_end = min(r_begin + a.rows_per_cta, a.n);
@@ -417,6 +436,7 @@ k_dense_tn(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUte
             mbar_init(empty0 + 8 * s, 1);
         }
         mbar_init(acc_full, 1);
+        mbar_init(acc_empty, 128);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -447,7 +467,9 @@ k_dense_tn(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUte
             const uint32_t idesc = umma_idesc_tf32_mn(a.n_pad);
             for (int i = 0; i < nslabs && ok; ++i) {
                 const int s = i % TN_STAGES, u = i / TN_STAGES;
-                ok = mbar_wait(ready0 + 8 * s, u & 1);
+                const int grp = i / T, in_grp = i % T;            // the accumulators restart with every flush group
+                if (in_grp == 0 && grp > 0) ok = mbar_wait(acc_empty, (grp - 1) & 1);
+                if (ok) ok = mbar_wait(ready0 + 8 * s, u & 1);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t st = base + s * stage_bytes;
@@ -459,20 +481,22 @@ k_dense_tn(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUte
 #pragma unroll
                     for (int k = 0; k < TN_ROWS / 8; ++k) {       // one 8-row group (1024 bytes) per MMA
                         const uint64_t adv = (uint64_t)(k * (1024 >> 4));
-                        umma_tf32(acc, x_tail + adv, g_head + adv, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                        umma_tf32(acc, x_tail + adv, g_head + adv, idesc, (in_grp > 0 || k > 0) ? 1u : 0u);
                         umma_tf32(acc, x_head + adv, g_tail + adv, idesc, 1u);
                         umma_tf32(acc, x_head + adv, g_head + adv, idesc, 1u);
                     }
                 }
                 umma_commit(empty0 + 8 * s);
+                if (in_grp == T - 1 || i == nslabs - 1) umma_commit(acc_full);
             }
-            if (ok) umma_commit(acc_full);
         }
     } else {
         const int t = threadIdx.x - 64;
+        const int q = warp & 3;                                   // the quarter of the tensor-memory lanes this warp may read
+        float4* part4 = reinterpret_cast<float4*>(a.partial + (size_t)blockIdx.x * a.m_halves * 128 * a.n_pad) + q * 32 + lane;
         for (int i = 0; i < nslabs && ok; ++i) {
             const int s = i % TN_STAGES, u = i / TN_STAGES;
-            ok = mbar_wait(full0 + 8 * s, u & 1);
+            ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, u & 1));        // warp-uniform: tcgen05.ld below is .aligned
             if (!ok) break;
             unsigned char* st = gbase + (size_t)s * stage_bytes;
             for (int part = 0; part < 2; ++part) {                // X then G: head in place, tail behind it
@@ -490,33 +514,42 @@ k_dense_tn(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUte
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(ready0 + 8 * s);
-        }
-        if (ok && nslabs > 0) ok = mbar_wait(acc_full, 0);
-        ok = __all_sync(0xffffffffu, ok);
-        const int q = warp & 3;
-        float* out = a.partial + (size_t)blockIdx.x * a.Km * a.Nn;
-        for (int h = 0; h < a.m_halves; ++h) {
-            const int row = h * 128 + q * 32 + lane;              // row of D = column of X
-            for (int c0 = 0; c0 < a.n_pad; c0 += 16) {
-                uint32_t r[16];
-                if (ok && nslabs > 0) {
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    asm volatile(
-                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                        : "r"(tmem + (uint32_t)(h * 256) + ((uint32_t)(q * 32) << 16) + (uint32_t)c0));
+            if (i % T != T - 1 && i != nslabs - 1) continue;
+            // Flush: the tensor cores add into their accumulator with truncation, an error that grows with the length
+            // of the chain, so after T slabs the accumulators are added - rounded to nearest - into this CTA's partial
+            // result (which stays in L2) and restart from zero.
+            const int grp = i / T;
+            ok = __all_sync(0xffffffffu, mbar_wait(acc_full, grp & 1));
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            for (int h = 0; h < a.m_halves; ++h) {
+                for (int c0 = 0; c0 < a.n_pad; c0 += 32) {        // two 16-column reads in flight per wait
+                    const int two = c0 + 16 < a.n_pad;            // warp-uniform
+                    uint32_t r[32];
+                    tmem_ld16(tmem + (uint32_t)(h * 256) + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+                    if (two) tmem_ld16(tmem + (uint32_t)(h * 256) + ((uint32_t)(q * 32) << 16) + (uint32_t)(c0 + 16), r + 16);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                } else {
+                    float4* p = part4 + (size_t)(h * (a.n_pad >> 4) + (c0 >> 4)) * 4 * 128;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) r[j] = 0u;       // a CTA without rows contributes zeros
-                }
-                if (row < a.Km) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (c0 + j < a.Nn) out[(size_t)row * a.Nn + c0 + j] = __uint_as_float(r[j]);
+                    for (int j = 0; j < 8; ++j) {
+                        if (j >= 4 && !two) break;
+                        // Only this thread ever touches these 16 bytes, in program order, so the sum order is fixed; the
+                        // reduction is sent to L2 and not waited for.
+                        if (grp == 0)
+                            __stcg(p + j * 128, make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                            __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+                        else
+                            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p + j * 128), "f"(__uint_as_float(r[4 * j])),
+                                         "f"(__uint_as_float(r[4 * j + 1])), "f"(__uint_as_float(r[4 * j + 2])), "f"(__uint_as_float(r[4 * j + 3]))
+                                         : "memory");
+                    }
                 }
             }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(acc_empty);
+        }
+        if (nslabs == 0) {                                        // a CTA without rows contributes zeros
+            for (int j = 0; j < a.m_halves * a.n_pad / 4; ++j) __stcg(part4 + (size_t)j * 128, make_float4(0.f, 0.f, 0.f, 0.f));
         }
     }
     if (!ok) atomicExch(a.status, 1);
@@ -526,13 +559,20 @@ k_dense_tn(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUte
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
 }
 
-__global__ void k_dense_tn_reduce(const float* __restrict__ partial, int n_parts, int64_t elems, float* __restrict__ D, int64_t ldd, int32_t Nn)
+// One thread per slot of the partial layout (coalesced over the CTAs' partials); slots of the padding are skipped.
+__global__ void k_dense_tn_reduce(const float* __restrict__ partial, int n_parts, int64_t slots, float* __restrict__ D, int64_t ldd,
+                                  int32_t Km, int32_t Nn, int32_t n_pad)
 {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= elems) return;
+    if (i >= slots) return;
+    const int e = (int)(i & 3), r = (int)((i >> 2) & 127);
+    const int64_t blk = i >> 9;                                   // (half, 16-column group, float4 within the group)
+    const int j4 = (int)(blk & 3), c16 = (int)((blk >> 2) % (n_pad >> 4)), h = (int)((blk >> 2) / (n_pad >> 4));
+    const int m = h * 128 + r, c = c16 * 16 + j4 * 4 + e;
+    if (m >= Km || c >= Nn) return;
     float sum = 0.f;
-    for (int p = 0; p < n_parts; ++p) sum += partial[(size_t)p * elems + i];
-    D[(i / Nn) * ldd + (i % Nn)] = sum;
+    for (int p = 0; p < n_parts; ++p) sum += partial[(size_t)p * slots + i];
+    D[(int64_t)m * ldd + c] = sum;
 }
 
 int make_map_box(CUtensorMap* map, const float* ptr, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows)
@@ -563,14 +603,17 @@ extern "C" int dg_dense_tn(const float* X, int64_t ldx, const float* G, int64_t 
                            int32_t Km, int32_t Nn, float* scratch, int64_t scratch_floats, int32_t max_ctas, void* stream)
 {
     if (!X || !G || !D || !scratch) return DG_ERR_NULL;
-    if (ldd < Nn || max_ctas < 1) return DG_ERR_DIMS;
+    if (ldd < Nn || max_ctas < 1 || (reinterpret_cast<uintptr_t>(scratch) & 15)) return DG_ERR_DIMS;
     if (!dg_dense_tn_supported(n, Km, Nn, ldx, ldg, X, G)) return DG_ERR_UNSUPPORTED;
     DenseTnArgs a{};
     a.n = n; a.Km = Km; a.Nn = Nn; a.n_pad = (Nn + 15) / 16 * 16; a.m_halves = Km > 128 ? 2 : 1;
     const int64_t slabs = (n + TN_ROWS - 1) / TN_ROWS;
     const int ctas = (int)std::min<int64_t>(max_ctas, slabs);
     a.rows_per_cta = (slabs + ctas - 1) / ctas * TN_ROWS;
-    if ((int64_t)ctas * Km * Nn > scratch_floats) return DG_ERR_SCRATCH;
+    const int64_t slots = (int64_t)a.m_halves * 128 * a.n_pad;    // one CTA's partial, padding included
+    if (ctas * slots > scratch_floats) return DG_ERR_SCRATCH;
+    static const int flush_env = [] { const char* v = getenv("DG_DENSE_TN_FLUSH"); return v ? atoi(v) : 0; }();
+    a.flush_slabs = flush_env > 0 ? flush_env : 16;               // 256 rows = 96 tensor-core accumulations per chain
     a.partial = scratch;
     a.status = dense_status_word();
     if (!a.status) return DG_ERR_STATE;
@@ -578,10 +621,9 @@ extern "C" int dg_dense_tn(const float* X, int64_t ldx, const float* G, int64_t 
     int rc;
     if ((rc = make_map_box(&tmX, X, n, Km, ldx, 32, TN_ROWS)) || (rc = make_map_box(&tmG, G, n, Nn, ldg, 32, TN_ROWS))) return rc;
     const int x_bytes = a.m_halves * 4 * TN_BOX_BYTES, g_bytes = (a.n_pad + 31) / 32 * TN_BOX_BYTES;
-    const size_t smem = (size_t)TN_STAGES * (2 * x_bytes + 2 * g_bytes) + 24 * TN_STAGES + 16 + 1024;
+    const size_t smem = (size_t)TN_STAGES * (2 * x_bytes + 2 * g_bytes) + 24 * TN_STAGES + 24 + 1024;
     DG_CUDA(cudaFuncSetAttribute(k_dense_tn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     k_dense_tn<<<ctas, kThreads, smem, (cudaStream_t)stream>>>(tmX, tmG, a);
-    const int64_t elems = (int64_t)Km * Nn;
-    k_dense_tn_reduce<<<(unsigned)((elems + 255) / 256), 256, 0, (cudaStream_t)stream>>>(scratch, ctas, elems, D, ldd, Nn);
+    k_dense_tn_reduce<<<(unsigned)((slots + 255) / 256), 256, 0, (cudaStream_t)stream>>>(scratch, ctas, slots, D, ldd, Km, Nn, a.n_pad);
     return (int)cudaGetLastError();
 }

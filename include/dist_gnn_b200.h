@@ -199,8 +199,11 @@ int dg_dense_nt(const float* A, int64_t lda, const float* Bt_head, const float* 
                 int64_t M, int32_t N, int32_t K, int32_t relu, void* stream);
 /* Weight-gradient product D[Km x Nn] = X[n x Km]^T * G[n x Nn] (torch.mm at models/gcn.py:50), same arithmetic (three
  * TF32 passes, fp32 accumulator in tensor memory) with BOTH operands split inside the kernel.  The n rows are shared
- * out over at most max_ctas CTAs; every CTA leaves a partial Km x Nn result in `scratch` (needs ctas * Km * Nn floats,
- * DG_ERR_SCRATCH otherwise) and a second kernel adds the partials in CTA order, so the result is bit-reproducible.
+ * out over at most max_ctas CTAs.  The tensor cores truncate when they add into their accumulator, an error that grows
+ * with the number of rows, so every 256 rows (environment DG_DENSE_TN_FLUSH, in 16-row slabs) a CTA adds its
+ * accumulators, rounded to nearest, into its partial result in `scratch` and restarts them; a second kernel adds the
+ * partials in CTA order, so the result is bit-reproducible and within about 6e-6 of the exact product for any n.
+ * `scratch` is 16-byte aligned and holds ctas * roundup(Km, 128) * roundup(Nn, 16) floats (DG_ERR_SCRATCH otherwise).
  * Limits: Km, Nn <= 256, n < 2^31, ldx and ldg multiples of 4 floats, X / G 16-byte aligned. */
 int dg_dense_tn_supported(int64_t n, int32_t Km, int32_t Nn, int64_t ldx, int64_t ldg, const void* X, const void* G);
 int dg_dense_tn(const float* X, int64_t ldx, const float* G, int64_t ldg, float* D, int64_t ldd, int64_t n, int32_t Km,
