@@ -262,7 +262,10 @@ def measure_stage_loops(env, g, widths, spmm_cpp):
     roots = [st.root_in_group for st in stages]
     n = g.local_num_nodes
     out = {'stage_group': group, 'stage_order': env.stage_order}
-    for width in widths:
+    from models import gcn as gcn_module
+    for true_width in widths:
+        # the model pads operand rows to a multiple of 4 floats before the stage loop; measure what it runs
+        width = true_width + (-true_width) % 4 if gcn_module.PAD_ODD_WIDTHS else true_width
         x = torch.randn(n, width, device=env.device)
         z = torch.empty_like(x)
         for timed in (False, True):
@@ -284,7 +287,8 @@ def measure_stage_loops(env, g, widths, spmm_cpp):
         dist.all_reduce(vals, op=dist.ReduceOp.MAX, group=env.world_group)
         comm_ms, spmm_ms, total_ms = vals.tolist()
         received = sum(1 for st in stages if st.root_in_group != env.col_comm.rank) * n * width * 4
-        out[f'F{width}'] = {
+        out[f'F{true_width}'] = {
+            'width_on_the_wire': width,
             'bcast_bus_gbs': round(len(stages) * n * width * 4 / (comm_ms * 1e-3) / 1e9, 2) if comm_ms > 0 else None,
             'bcast_frac_of_900': round(len(stages) * n * width * 4 / (comm_ms * 1e-3) / 1e9 / 900.0, 4) if comm_ms > 0 else None,
             'comm_ms': round(comm_ms, 4), 'spmm_ms': round(spmm_ms, 4), 'loop_ms': round(total_ms, 4),

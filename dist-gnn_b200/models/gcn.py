@@ -35,6 +35,14 @@ def spmm(A, B, C):
 #             is dropped).  About 5e-7 relative error per product - inside the 1e-5 parity bound - at a fraction of the
 #             CUDA-core time, because these skinny GEMMs are then bound by reading the activations.
 DENSE_MODE = os.environ.get('DIST_GNN_DENSE', 'tcgen05')
+PAD_ODD_WIDTHS = os.environ.get('DIST_GNN_PAD_WIDTHS', '1') != '0'
+
+
+def _rows(t):
+    """t itself when its rows are dense and start on 16-byte boundaries (a column slice of a padded buffer), else a copy."""
+    if t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 4 == 0 and t.stride(0) >= t.size(1) and t.data_ptr() % 16 == 0:
+        return t
+    return t.contiguous()
 
 
 def _tf32_split(x):
@@ -46,11 +54,11 @@ def dense_mm(a, b, ta=False, tb=False):
     """op(a) @ op(b) for fp32 CUDA matrices according to DENSE_MODE; ta / tb transpose the (contiguous) operand."""
     if DENSE_MODE == 'tcgen05' and a.is_cuda and not ta:
         # hand-written tensor-core kernel: a [M x K] times a small matrix given as bt [N x K]; other shapes fall through
-        out = spmm_cpp.dense_nt(a.contiguous(), b.contiguous() if tb else b.t().contiguous())
+        out = spmm_cpp.dense_nt(_rows(a), b.contiguous() if tb else b.t().contiguous())
         if out is not None:
             return out
     if DENSE_MODE == 'tcgen05' and a.is_cuda and ta and not tb:
-        out = spmm_cpp.dense_tn(a.contiguous(), b.contiguous())      # a^T @ b with the reduction over the shared rows
+        out = spmm_cpp.dense_tn(_rows(a), _rows(b))                  # a^T @ b with the reduction over the shared rows
         if out is not None:
             return out
     if DENSE_MODE != '3xtf32' or not a.is_cuda:
@@ -76,10 +84,26 @@ def broadcast(local_adj_parts, local_feature, tag):
     if not local_feature.is_cuda:
         raise RuntimeError('the broadcast-SpMM stage loop runs on CUDA tensors only; there is no CPU path')
     x = local_feature.contiguous()
+    true_width = x.size(1)
+    if true_width % 4 and PAD_ODD_WIDTHS:
+        # Rows that are not a whole number of 16-byte pieces (47 classes = 188 bytes) cannot be moved with 128-bit loads
+        # and start at odd offsets.  The stage loop then runs on a copy whose rows are padded with zero columns to the
+        # next multiple of 4; the caller gets the first true_width columns of the wider result.
+        wide = env.recv_buffers(x.size(0), true_width + (-true_width) % 4, nbuf=1, tag='padded')[0]
+        wide[:, :true_width] = x
+        wide[:, true_width:] = 0
+        x = wide
     n, width = x.shape
     stages = env.stages()
     comm = env.col_comm
     z = torch.empty_like(x)
+    if width != true_width:
+        return _stage_loop(env, local_adj_parts, x, z, stages, comm)[:, :true_width]
+    return _stage_loop(env, local_adj_parts, x, z, stages, comm)
+
+
+def _stage_loop(env, local_adj_parts, x, z, stages, comm):
+    n, width = x.shape
     if comm is not None and env.stage_order == 'feature_chunks' and env.rep == 1:
         # 1D only: pipeline along the feature dimension (all-gather of column chunks, full-length rows per product)
         plan = group_plans(local_adj_parts, [st.part for st in stages], len(stages))[0]

@@ -106,6 +106,16 @@ def _dev_tensor(t, dtype, what):
     return t
 
 
+def _row_major(t, what):
+    """Row stride (in floats) of a 2-D fp32 CUDA matrix whose rows are dense but may lie further apart than their
+    length - a column slice of a wider buffer, as the stage loop returns for operands it padded."""
+    if not (isinstance(t, torch.Tensor) and t.is_cuda):
+        raise RuntimeError(f'{what} must be a CUDA tensor: this library has no CPU path')
+    if t.dtype != torch.float32 or t.dim() != 2 or (t.size(1) > 1 and t.stride(1) != 1) or (t.size(0) > 1 and t.stride(0) < t.size(1)):
+        raise RuntimeError(f'{what} must be a row-major fp32 matrix, got {t.dtype} {tuple(t.shape)} strides {t.stride()}')
+    return t.stride(0) if t.size(0) > 1 else max(t.size(1), 1)
+
+
 class SpmmPlan:
     """Device CSR plan of one sparse block (dg_plan).  Keeps the int32 column ids and fp32 values alive."""
 
@@ -383,17 +393,23 @@ def dense_split(w):
 def dense_nt(a, bt, relu=False):
     """a [M x K] @ bt[N x K]^T on the tensor cores with fp32 accuracy (dg_dense_nt), or None when the shapes or strides
     are outside what the kernel takes (the caller then uses a library GEMM)."""
-    _dev_tensor(a, torch.float32, 'a'), _dev_tensor(bt, torch.float32, 'bt')
+    lda = _row_major(a, 'a')
+    _dev_tensor(bt, torch.float32, 'bt')
     M, K = a.shape
     N = bt.size(0)
     if bt.size(1) != K:
         raise RuntimeError(f'inner dimensions differ: {tuple(a.shape)} x {tuple(bt.shape)}^T')
-    if M == 0 or not lib().dg_dense_supported(M, N, K, K, K, a.data_ptr(), bt.data_ptr(), bt.data_ptr()):
+    if K % 4:                       # the small operand is re-laid with a row stride the tensor maps accept; K itself stays
+        wide = torch.zeros((N, K + (-K) % 4), dtype=torch.float32, device=bt.device)
+        wide[:, :K] = bt
+        bt = wide
+    ldb = bt.size(1)
+    if M == 0 or not lib().dg_dense_supported(M, N, K, lda, ldb, a.data_ptr(), bt.data_ptr(), bt.data_ptr()):
         return None
     head, tail = dense_split(bt)
     c = torch.empty((M, N), dtype=torch.float32, device=a.device)
     with torch.cuda.device(a.device):
-        check(lib().dg_dense_nt(a.data_ptr(), K, head.data_ptr(), tail.data_ptr(), K, c.data_ptr(), N, M, N, K, int(relu), _stream()))
+        check(lib().dg_dense_nt(a.data_ptr(), lda, head.data_ptr(), tail.data_ptr(), ldb, c.data_ptr(), N, M, N, K, int(relu), _stream()))
     return c
 
 
@@ -403,12 +419,12 @@ _tn_scratch = {}
 def dense_tn(x, g):
     """x[n x Km]^T @ g[n x Nn] on the tensor cores with fp32 accuracy (dg_dense_tn), or None when the shapes or strides
     are outside what the kernel takes.  Both operands are streamed once; per-CTA partial results are added in CTA order."""
-    _dev_tensor(x, torch.float32, 'x'), _dev_tensor(g, torch.float32, 'g')
+    ldx, ldg = _row_major(x, 'x'), _row_major(g, 'g')
     n, Km = x.shape
     Nn = g.size(1)
     if g.size(0) != n:
         raise RuntimeError(f'row counts differ: {tuple(x.shape)} vs {tuple(g.shape)}')
-    if n == 0 or not lib().dg_dense_tn_supported(n, Km, Nn, Km, Nn, x.data_ptr(), g.data_ptr()):
+    if n == 0 or not lib().dg_dense_tn_supported(n, Km, Nn, ldx, ldg, x.data_ptr(), g.data_ptr()):
         return None
     ctas = torch.cuda.get_device_properties(x.device).multi_processor_count
     scratch = _tn_scratch.get(x.device)
@@ -416,7 +432,7 @@ def dense_tn(x, g):
         scratch = _tn_scratch[x.device] = torch.empty(ctas * 256 * 256, dtype=torch.float32, device=x.device)
     d = torch.empty((Km, Nn), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
-        check(lib().dg_dense_tn(x.data_ptr(), Km, g.data_ptr(), Nn, d.data_ptr(), Nn, n, Km, Nn, scratch.data_ptr(), scratch.numel(),
+        check(lib().dg_dense_tn(x.data_ptr(), ldx, g.data_ptr(), ldg, d.data_ptr(), Nn, n, Km, Nn, scratch.data_ptr(), scratch.numel(),
                                 ctas, _stream()))
     return d
 

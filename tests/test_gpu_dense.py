@@ -50,6 +50,43 @@ def test_dense_tn_matches_float64(n, Km, Nn):
     assert spmm_cpp.dense_status() == 0
 
 
+def test_dense_tn_error_does_not_grow_with_the_row_count():
+    """All-positive operands over the full benchmark row count: the worst case for the truncating tensor-core accumulator,
+    whose error without the periodic flush is 3e-4 here (and linear in the number of rows)."""
+    import spmm_cpp
+    n = 2449029
+    g = torch.Generator(device='cuda').manual_seed(5)
+    x = torch.rand(n, 256, device='cuda', generator=g)
+    y = torch.rand(n, 256, device='cuda', generator=g)
+    want = torch.zeros(256, 256, device='cuda', dtype=torch.float64)
+    for s in range(0, n, 200000):
+        want += x[s:s + 200000].double().t() @ y[s:s + 200000].double()
+    d = spmm_cpp.dense_tn(x, y)
+    assert_close(d.cpu().numpy(), want.cpu().numpy(), TOL, 'full-size weight gradient')
+    assert spmm_cpp.dense_status() == 0
+
+
+def test_dense_kernels_take_column_slices_of_padded_buffers():
+    """47 columns held in rows of 48 floats (what the stage loop returns for an odd class count): both products read the
+    slice in place and ignore the padding column."""
+    import spmm_cpp
+    n = 20000
+    g = torch.Generator(device='cuda').manual_seed(47)
+    wide = torch.randn(n, 48, device='cuda', generator=g)
+    ag = wide[:, :47]
+    w = torch.randn(256, 47, device='cuda', generator=g)          # layer weight [in x out]: dX = AG * W^T
+    h = torch.randn(n, 256, device='cuda', generator=g)
+    dx = spmm_cpp.dense_nt(ag, w)
+    assert dx is not None and dx.shape == (n, 256)
+    assert_close(dx.cpu().numpy(), (ag.double() @ w.double().t()).cpu().numpy(), TOL, 'dX from a 47-of-48 slice')
+    dw = spmm_cpp.dense_tn(h, ag)
+    assert dw is not None and dw.shape == (256, 47)
+    assert_close(dw.cpu().numpy(), (h.double().t() @ ag.double()).cpu().numpy(), TOL, 'dW from a 47-of-48 slice')
+    with pytest.raises(RuntimeError):
+        spmm_cpp.dense_tn(h, wide.t()[:47].t()[:, ::2])           # not row-major
+    assert spmm_cpp.dense_status() == 0
+
+
 def test_dense_tn_unsupported_shapes_fall_back():
     import spmm_cpp
     assert spmm_cpp.dense_tn(torch.randn(100, 47, device='cuda'), torch.randn(100, 16, device='cuda')) is None
