@@ -32,6 +32,8 @@ struct DenseArgs {
     int64_t M;
     int32_t N, K, n_pad;            // n_pad = N rounded up to 16 (UMMA N)
     uint32_t relu;
+    const float* mask;              // optional [M x N]: the result is zeroed where mask <= 0 (ReLU backward), else nullptr
+    int64_t ldm;
     int* status;
 };
 
@@ -215,7 +217,22 @@ k_dense_nt(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
             const int64_t row = m0 + q * 32 + lane;
             float* crow = a.C + row * a.ldc;
             const bool vec_ok = (a.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.C) & 15) == 0);
+            const bool mvec_ok = a.mask && (a.ldm % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.mask) & 15) == 0);
+            const float* mrow = a.mask ? a.mask + row * a.ldm : nullptr;
             for (int c0 = 0; c0 < a.n_pad; c0 += 16) {
+                float mk[16];
+                if (mrow && row < a.M) {                          // issued before the accumulator read so that both are in flight
+                    if (mvec_ok && c0 + 16 <= a.N) {
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4) {
+                            const float4 m4 = __ldg(reinterpret_cast<const float4*>(mrow + c0 + j));
+                            mk[j] = m4.x; mk[j + 1] = m4.y; mk[j + 2] = m4.z; mk[j + 3] = m4.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) mk[j] = c0 + j < a.N ? __ldg(mrow + c0 + j) : 0.f;
+                    }
+                }
                 uint32_t r[16];
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -229,6 +246,7 @@ k_dense_nt(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
                     for (int j = 0; j < 16; ++j) {
                         v[j] = __uint_as_float(r[j]);
                         if (a.relu) v[j] = fmaxf(v[j], 0.f);
+                        if (mrow && !(mk[j] > 0.f)) v[j] = 0.f;
                     }
                     if (vec_ok && c0 + 16 <= a.N) {
 #pragma unroll
@@ -329,11 +347,19 @@ extern "C" int dg_dense_supported(int64_t M, int32_t N, int32_t K, int64_t lda, 
 extern "C" int dg_dense_nt(const float* A, int64_t lda, const float* Bt_head, const float* Bt_tail, int64_t ldb, float* C,
                            int64_t ldc, int64_t M, int32_t N, int32_t K, int32_t relu, void* stream)
 {
+    return dg_dense_nt_masked(A, lda, Bt_head, Bt_tail, ldb, C, ldc, M, N, K, relu, nullptr, 0, stream);
+}
+
+extern "C" int dg_dense_nt_masked(const float* A, int64_t lda, const float* Bt_head, const float* Bt_tail, int64_t ldb, float* C,
+                                  int64_t ldc, int64_t M, int32_t N, int32_t K, int32_t relu, const float* mask, int64_t ldm,
+                                  void* stream)
+{
     if (!A || !Bt_head || !Bt_tail || !C) return DG_ERR_NULL;
-    if (ldc < N) return DG_ERR_DIMS;
+    if (ldc < N || (mask && ldm < N)) return DG_ERR_DIMS;
     if (!dg_dense_supported(M, N, K, lda, ldb, A, Bt_head, Bt_tail)) return DG_ERR_UNSUPPORTED;
     DenseArgs a{};
     a.C = C; a.ldc = ldc; a.M = M; a.N = N; a.K = K; a.n_pad = (N + 15) / 16 * 16; a.relu = relu ? 1u : 0u;
+    a.mask = mask; a.ldm = ldm;
     a.status = dense_status_word();
     if (!a.status) return DG_ERR_STATE;
     CUtensorMap tmA, tmBh, tmBt;

@@ -36,6 +36,7 @@ def spmm(A, B, C):
 #             CUDA-core time, because these skinny GEMMs are then bound by reading the activations.
 DENSE_MODE = os.environ.get('DIST_GNN_DENSE', 'tcgen05')
 PAD_ODD_WIDTHS = os.environ.get('DIST_GNN_PAD_WIDTHS', '1') != '0'
+FUSE_RELU = os.environ.get('DIST_GNN_FUSE_RELU', '1') != '0'
 
 
 def _rows(t):
@@ -50,17 +51,29 @@ def _tf32_split(x):
     return head, x - head
 
 
-def dense_mm(a, b, ta=False, tb=False):
-    """op(a) @ op(b) for fp32 CUDA matrices according to DENSE_MODE; ta / tb transpose the (contiguous) operand."""
+def dense_mm(a, b, ta=False, tb=False, relu=False, mask=None):
+    """op(a) @ op(b) for fp32 CUDA matrices according to DENSE_MODE; ta / tb transpose the (contiguous) operand.
+    relu applies max(x, 0) to the product; mask (same shape as the product) zeroes it where mask <= 0.  Both are fused
+    into the tensor-core kernel's epilogue and are separate passes on the library paths."""
     if DENSE_MODE == 'tcgen05' and a.is_cuda and not ta:
         # hand-written tensor-core kernel: a [M x K] times a small matrix given as bt [N x K]; other shapes fall through
-        out = spmm_cpp.dense_nt(_rows(a), b.contiguous() if tb else b.t().contiguous())
+        out = spmm_cpp.dense_nt(_rows(a), b.contiguous() if tb else b.t().contiguous(), relu=relu,
+                                mask=_rows(mask) if mask is not None else None)
         if out is not None:
             return out
-    if DENSE_MODE == 'tcgen05' and a.is_cuda and ta and not tb:
+    if DENSE_MODE == 'tcgen05' and a.is_cuda and ta and not tb and not relu and mask is None:
         out = spmm_cpp.dense_tn(_rows(a), _rows(b))                  # a^T @ b with the reduction over the shared rows
         if out is not None:
             return out
+    out = _library_mm(a, b, ta, tb)
+    if relu:
+        out = out.relu_()
+    if mask is not None:
+        out = out.mul_(mask > 0)
+    return out
+
+
+def _library_mm(a, b, ta, tb):
     if DENSE_MODE != '3xtf32' or not a.is_cuda:
         return torch.mm(a.t() if ta else a, b.t() if tb else b)
     (ah, at), (bh, bt) = _tf32_split(a), _tf32_split(b)
@@ -178,13 +191,22 @@ def group_plans(adj_parts, parts, group):
 
 
 class DistGCNLayer(torch.autograd.Function):
+    """forward(features, weight, adj_parts, tag) as in the reference (gcn.py:35-53).  Two optional flags let GCN fuse the
+    ReLU between two layers into the dense kernels instead of running it (and its backward) as separate passes:
+
+    relu            the layer returns max(out, 0).  Its backward then expects a grad_output that is ALREADY zero where
+                    the returned activation is zero - which is what the next layer delivers when it is called with
+    input_is_relu   this layer's input is such an activation: the gradient it returns for the input is zeroed where
+                    the input is <= 0 (the ReLU's backward, applied in the epilogue of AG * W^T).
+    Used as a pair they compute exactly  relu(layer(x))  and its gradient; one without the other does not."""
+
     @staticmethod
-    def forward(ctx, features, weight, adj_parts, tag):
+    def forward(ctx, features, weight, adj_parts, tag, relu=False, input_is_relu=False):
         ctx.save_for_backward(features, weight)
-        ctx.adj_parts, ctx.tag = adj_parts, tag
+        ctx.adj_parts, ctx.tag, ctx.input_is_relu = adj_parts, tag, input_is_relu
         z_local = broadcast(adj_parts, features, 'Forward' + tag)
         with DistEnv.env.timer.timing_cuda('mm'):
-            z_local = dense_mm(z_local, weight)
+            z_local = dense_mm(z_local, weight, relu=relu)
         return z_local
 
     @staticmethod
@@ -192,16 +214,20 @@ class DistGCNLayer(torch.autograd.Function):
         features, weight = ctx.saved_tensors
         ag = broadcast(ctx.adj_parts, grad_output, 'Backward' + ctx.tag)
         with DistEnv.env.timer.timing_cuda('mm'):
-            grad_features = dense_mm(ag, weight, tb=True) if ctx.needs_input_grad[0] else None
+            grad_features = None
+            if ctx.needs_input_grad[0]:
+                grad_features = dense_mm(ag, weight, tb=True, mask=features if ctx.input_is_relu else None)
             grad_weight = dense_mm(features, ag, ta=True)
         with DistEnv.env.timer.timing_cuda('all_reduce'):
             DistEnv.env.all_reduce_sum(grad_weight)
-        return grad_features, grad_weight, None, None
+        return grad_features, grad_weight, None, None, None, None
 
 
 class GCN(nn.Module):
     """num_layers DistGCNLayers with ReLU between them, no bias (gcn.py:56-72).  Weights are drawn as the reference
-    draws them - torch.rand on the host after manual_seed(0), layer by layer - unless `weights` injects them."""
+    draws them - torch.rand on the host after manual_seed(0), layer by layer - unless `weights` injects them.
+    The ReLUs run inside the dense kernels (FUSE_RELU); with DIST_GNN_FUSE_RELU=0 they are F.relu calls as in the
+    reference."""
 
     def __init__(self, g, env, hidden_dim=16, num_layers=3, weights=None):
         super().__init__()
@@ -219,8 +245,12 @@ class GCN(nn.Module):
 
     def forward(self, features):
         h = features
+        last = self.num_layers - 1
         for l, w in enumerate(self.weights()):
-            h = DistGCNLayer.apply(h, w, self.g.adj_parts, f'L{l + 1}')
-            if l < self.num_layers - 1:
-                h = F.relu(h)
+            if FUSE_RELU:
+                h = DistGCNLayer.apply(h, w, self.g.adj_parts, f'L{l + 1}', l < last, l > 0)
+            else:
+                h = DistGCNLayer.apply(h, w, self.g.adj_parts, f'L{l + 1}')
+                if l < last:
+                    h = F.relu(h)
         return h

@@ -76,6 +76,7 @@ def lib():
             'dg_dense_split': ([vp, vp, vp, i64, vp], ctypes.c_int),
             'dg_dense_supported': ([i64, i32, i32, i64, i64, vp, vp, vp], ctypes.c_int),
             'dg_dense_nt': ([vp, i64, vp, vp, i64, vp, i64, i64, i32, i32, i32, vp], ctypes.c_int),
+            'dg_dense_nt_masked': ([vp, i64, vp, vp, i64, vp, i64, i64, i32, i32, i32, vp, i64, vp], ctypes.c_int),
             'dg_dense_tn_supported': ([i64, i32, i32, i64, i64, vp, vp], ctypes.c_int),
             'dg_dense_tn': ([vp, i64, vp, i64, vp, i64, i64, i32, i32, vp, i64, i32, vp], ctypes.c_int),
             'dg_dense_status': ([ctypes.POINTER(ctypes.c_int), vp], ctypes.c_int),
@@ -390,10 +391,14 @@ def dense_split(w):
     return head, tail
 
 
-def dense_nt(a, bt, relu=False):
+def dense_nt(a, bt, relu=False, mask=None):
     """a [M x K] @ bt[N x K]^T on the tensor cores with fp32 accuracy (dg_dense_nt), or None when the shapes or strides
-    are outside what the kernel takes (the caller then uses a library GEMM)."""
+    are outside what the kernel takes (the caller then uses a library GEMM).  relu applies max(x, 0) on the way out;
+    mask [M x N] zeroes the result where mask <= 0 (the backward of a ReLU whose output is `mask`)."""
     lda = _row_major(a, 'a')
+    ldm = _row_major(mask, 'mask') if mask is not None else 0
+    if mask is not None and tuple(mask.shape) != (a.size(0), bt.size(0)):
+        raise RuntimeError(f'mask is {tuple(mask.shape)}, the product {(a.size(0), bt.size(0))}')
     _dev_tensor(bt, torch.float32, 'bt')
     M, K = a.shape
     N = bt.size(0)
@@ -409,7 +414,8 @@ def dense_nt(a, bt, relu=False):
     head, tail = dense_split(bt)
     c = torch.empty((M, N), dtype=torch.float32, device=a.device)
     with torch.cuda.device(a.device):
-        check(lib().dg_dense_nt(a.data_ptr(), lda, head.data_ptr(), tail.data_ptr(), ldb, c.data_ptr(), N, M, N, K, int(relu), _stream()))
+        check(lib().dg_dense_nt_masked(a.data_ptr(), lda, head.data_ptr(), tail.data_ptr(), ldb, c.data_ptr(), N, M, N, K, int(relu),
+                                       mask.data_ptr() if mask is not None else None, ldm, _stream()))
     return c
 
 

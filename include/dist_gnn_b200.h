@@ -197,6 +197,12 @@ int dg_dense_split(const float* src, float* head, float* tail, int64_t count, vo
 int dg_dense_supported(int64_t M, int32_t N, int32_t K, int64_t lda, int64_t ldb, const void* A, const void* Bt_head, const void* Bt_tail);
 int dg_dense_nt(const float* A, int64_t lda, const float* Bt_head, const float* Bt_tail, int64_t ldb, float* C, int64_t ldc,
                 int64_t M, int32_t N, int32_t K, int32_t relu, void* stream);
+/* The same product with the derivative of a ReLU applied on the way out: element (i, j) is zeroed where
+ * mask[i * ldm + j] <= 0 (mask = the activation the gradient flows back through; the `grad * (h > 0)` that autograd runs
+ * as a separate pass after torch.mm at models/gcn.py:49).  mask == NULL is dg_dense_nt. */
+int dg_dense_nt_masked(const float* A, int64_t lda, const float* Bt_head, const float* Bt_tail, int64_t ldb, float* C,
+                       int64_t ldc, int64_t M, int32_t N, int32_t K, int32_t relu, const float* mask, int64_t ldm,
+                       void* stream);
 /* Weight-gradient product D[Km x Nn] = X[n x Km]^T * G[n x Nn] (torch.mm at models/gcn.py:50), same arithmetic (three
  * TF32 passes, fp32 accumulator in tensor memory) with BOTH operands split inside the kernel.  The n rows are shared
  * out over at most max_ctas CTAs.  The tensor cores truncate when they add into their accumulator, an error that grows

@@ -66,6 +66,23 @@ def test_dense_tn_error_does_not_grow_with_the_row_count():
     assert spmm_cpp.dense_status() == 0
 
 
+@pytest.mark.parametrize('M,N,K', [(1000, 256, 256), (777, 100, 48), (130, 47, 256)])
+def test_dense_nt_mask_zeroes_where_the_activation_is_zero(M, N, K):
+    import spmm_cpp
+    g = torch.Generator(device='cuda').manual_seed(M + N)
+    a = torch.randn(M, K, device='cuda', generator=g)
+    bt = torch.randn(N, K, device='cuda', generator=g)
+    act = torch.relu(torch.randn(M, N, device='cuda', generator=g))       # about half zeros, like a ReLU output
+    out = spmm_cpp.dense_nt(a, bt, mask=act)
+    plain = spmm_cpp.dense_nt(a, bt)
+    assert out is not None and plain is not None
+    assert torch.equal(out, plain * (act > 0))
+    want = (a.double() @ bt.double().t()) * (act > 0)
+    assert_close(out.cpu().numpy(), want.cpu().numpy(), TOL, f'masked {M}x{N}x{K}')
+    with pytest.raises(RuntimeError):
+        spmm_cpp.dense_nt(a, bt, mask=act[:, :-1])
+
+
 def test_dense_kernels_take_column_slices_of_padded_buffers():
     """47 columns held in rows of 48 floats (what the stage loop returns for an odd class count): both products read the
     slice in place and ignore the padding column."""

@@ -203,3 +203,31 @@ def test_full_size_graph_and_spmm_properties(big_graph):
             block = block[:part.size(1)]
         spmm_cpp.SpmmPlan.from_coo(part).spmm(block, Z, 1.0, 0.0 if s == 0 else 1.0)
     assert (Z - AX).abs().max().item() <= 1e-5 * scale
+
+
+def test_fused_relu_equals_separate_relu(golden, env1):
+    """The ReLU between two layers, run inside the dense kernels' epilogues (forward: max(x, 0); backward: the gradient
+    zeroed where the activation is zero), gives bit-identical logits and weight gradients to F.relu between the layers."""
+    from coo_graph import COO_Graph, Parted_COO_Graph
+    from models import gcn as gcn_module
+    from models import GCN
+    z = golden('graph_small')
+    full = COO_Graph.from_dict('gsmall', _fixture_dataset(z), device='cuda')
+    g = Parted_COO_Graph.from_full(full, 0, 1)
+    gen = torch.Generator().manual_seed(3)
+    weights = [torch.randn(32, 64, generator=gen) * 0.3, torch.randn(64, 64, generator=gen) * 0.3, torch.randn(64, 7, generator=gen) * 0.3]
+    results = {}
+    saved = gcn_module.FUSE_RELU
+    try:
+        for fused in (True, False):
+            gcn_module.FUSE_RELU = fused
+            model = GCN(g, env1, hidden_dim=64, num_layers=3, weights=weights)
+            out = model(g.features)
+            (out * torch.linspace(-1, 1, out.numel(), device=out.device).view_as(out)).sum().backward()
+            results[fused] = (out.detach().clone(), [w.grad.detach().clone() for w in model.weights()])
+    finally:
+        gcn_module.FUSE_RELU = saved
+    assert torch.equal(results[True][0], results[False][0])
+    assert (results[True][0] != 0).any()
+    for a, b in zip(results[True][1], results[False][1]):
+        assert torch.equal(a, b)
