@@ -41,7 +41,7 @@ def parse():
     ap.add_argument('--layers', type=int, default=0, help='override the number of GCN layers')
     ap.add_argument('--seed', type=int, default=0)
     ap.add_argument('--stage-group', type=int, default=0, help='stages fused into one product (0 = the default of DistEnv)')
-    ap.add_argument('--stage-order', default=None, choices=['reference', 'local_first', 'feature_chunks'],
+    ap.add_argument('--stage-order', default=None, choices=['reference', 'local_first', 'feature_chunks', 'peer_copy'],
                     help='order of the products inside a distributed SpMM (default: that of DistEnv)')
     ap.add_argument('--chunk-width', type=int, default=0, help='column chunk width of the feature_chunks order (0 = default 64)')
     ap.add_argument('--dense', default=None, choices=['fp32', '3xtf32', 'tcgen05'],
@@ -274,6 +274,10 @@ def measure_stage_loops(env, g, widths, spmm_cpp):
                 chunks = spmm_cpp.chunk_widths(width, env.chunk_width)
                 spmm_cpp.allgather_spmm(env.col_comm, plan, x, env.recv_buffers(n, max(chunks), tag='pack'),
                                         env.recv_buffers(n * env.col_comm.size, max(chunks), tag='area'), z, chunks, timed=timed)
+            elif env.stage_order == 'peer_copy':
+                env.ensure_peer_buffers(n * width)
+                spmm_cpp.peer_spmm(env.col_comm, *ordered_products(env, g.adj_parts, stages, x, rotate=True), x, z,
+                                   row_comm=env.row_comm, timed=timed)
             elif env.stage_order == 'local_first':
                 spmm_cpp.bcast_spmm_ordered(env.col_comm, *ordered_products(env, g.adj_parts, stages, x), x, z,
                                             row_comm=env.row_comm, timed=timed, bcast_group=env.stage_group)
@@ -287,10 +291,11 @@ def measure_stage_loops(env, g, widths, spmm_cpp):
         dist.all_reduce(vals, op=dist.ReduceOp.MAX, group=env.world_group)
         comm_ms, spmm_ms, total_ms = vals.tolist()
         received = sum(1 for st in stages if st.root_in_group != env.col_comm.rank) * n * width * 4
+        moved = received if env.stage_order == 'peer_copy' else len(stages) * n * width * 4     # peer copies move remote blocks only
         out[f'F{true_width}'] = {
             'width_on_the_wire': width,
-            'bcast_bus_gbs': round(len(stages) * n * width * 4 / (comm_ms * 1e-3) / 1e9, 2) if comm_ms > 0 else None,
-            'bcast_frac_of_900': round(len(stages) * n * width * 4 / (comm_ms * 1e-3) / 1e9 / 900.0, 4) if comm_ms > 0 else None,
+            'bcast_bus_gbs': round(moved / (comm_ms * 1e-3) / 1e9, 2) if comm_ms > 0 else None,
+            'bcast_frac_of_900': round(moved / (comm_ms * 1e-3) / 1e9 / 900.0, 4) if comm_ms > 0 else None,
             'comm_ms': round(comm_ms, 4), 'spmm_ms': round(spmm_ms, 4), 'loop_ms': round(total_ms, 4),
             'overlap': round((comm_ms + spmm_ms - total_ms) / max(min(comm_ms, spmm_ms), 1e-9), 4),
             'received_bytes': received,

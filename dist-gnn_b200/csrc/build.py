@@ -9,7 +9,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-SOURCES = ['dg_plan.cu', 'dg_spmm.cu', 'dg_spmm_stream.cu', 'dg_spmm_static.cu', 'dg_dense.cu', 'dg_pipeline.cu']
+SOURCES = ['dg_plan.cu', 'dg_spmm.cu', 'dg_spmm_stream.cu', 'dg_spmm_static.cu', 'dg_dense.cu', 'dg_pipeline.cu', 'dg_peer.cu']
 OUTPUT = os.path.join(HERE, 'libdist_gnn_b200.so')
 
 

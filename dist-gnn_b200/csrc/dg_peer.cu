@@ -1,0 +1,248 @@
+// Distributed product whose remote blocks are PULLED over NVLink by the copy engines instead of broadcast by NCCL.
+//
+// Replaces the same stage loop of the reference (light_dist_gnn/models/gcn.py:16-30; 1.5D: 1D_CAGNET/dist_15d.py:61-106)
+// as dg_bcast_spmm_ordered, with one difference in how a block travels: every rank keeps two send buffers that its
+// peers have mapped through CUDA IPC.  Per distributed product a rank copies its block into the send buffer of this
+// product, all ranks meet in a one-float all-reduce on the side stream (the only collective: it orders "every block is
+// in place" before "anyone reads"), and then each rank issues one device-to-device copy per remote block it needs,
+// straight from the owner's send buffer into its own receive area.  The copies run on the DMA engines: they take no
+// SMs from the products that run beside them, need no matching call on the owner's side, and each block's arrival
+// releases the product that reads it.  Nothing in here spins on the device; all ordering is stream order, events and
+// that one collective.
+//
+// Send buffer reuse: product k uses buffer k % 2.  Overwriting it at product k is safe once every peer has finished
+// the reads of product k-2, and a peer enters the all-reduce of product k-1 only after those reads (same stream), so
+// the completion of that all-reduce on this rank - which the compute stream waited for during product k-1 - is enough.
+#include <nccl.h>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+#include "dg_internal.h"
+#include "dg_comm.h"
+
+namespace {
+
+int peer_release(dg_comm* c)
+{
+    int first_error = DG_OK;
+    for (int r = 0; r < (int)c->peer_ptr.size() / 2; ++r) {
+        if (r == c->rank) continue;
+        for (int b = 0; b < 2; ++b) {
+            float* p = c->peer_ptr[2 * r + b];
+            if (p) {
+                cudaError_t e = cudaIpcCloseMemHandle(p);
+                if (e != cudaSuccess && first_error == DG_OK) first_error = (int)e;
+            }
+        }
+    }
+    c->peer_ptr.clear();
+    return first_error;
+}
+
+// One remote block, cut into `lanes` pieces that are copied concurrently (one copy engine does not fill the link):
+// piece 0 on the side stream, the others on lane streams that start after everything queued on the side stream so far
+// and that the side stream joins again afterwards, so that "arrived" on the side stream still means the whole block.
+int pull_block(dg_comm* c, float* dst, const float* src, size_t count, int lanes)
+{
+    int rc;
+    if (lanes > 1 && count >= (size_t)lanes * 65536) {
+        while ((int)c->peer_lanes.size() < lanes - 1) {
+            int prio_low = 0, prio_high = 0;
+            cudaStream_t st;
+            DG_CUDA(cudaDeviceGetStreamPriorityRange(&prio_low, &prio_high));
+            DG_CUDA(cudaStreamCreateWithPriority(&st, cudaStreamNonBlocking, prio_high));
+            c->peer_lanes.push_back(st);
+        }
+        if ((rc = make_events(c->ev_lane, (size_t)lanes, cudaEventDisableTiming))) return rc;
+        const size_t piece = ((count + lanes - 1) / lanes + 63) / 64 * 64;
+        DG_CUDA(cudaEventRecord(c->ev_lane[0], c->side));
+        for (int l = 1; l < lanes; ++l) {
+            const size_t a = (size_t)l * piece, e = a + piece < count ? a + piece : count;
+            if (a >= e) break;
+            cudaStream_t st = c->peer_lanes[l - 1];
+            DG_CUDA(cudaStreamWaitEvent(st, c->ev_lane[0], 0));
+            DG_CUDA(cudaMemcpyAsync(dst + a, src + a, (e - a) * sizeof(float), cudaMemcpyDeviceToDevice, st));
+            DG_CUDA(cudaEventRecord(c->ev_lane[l], st));
+        }
+        DG_CUDA(cudaMemcpyAsync(dst, src, (piece < count ? piece : count) * sizeof(float), cudaMemcpyDeviceToDevice, c->side));
+        for (int l = 1; l < lanes; ++l) {
+            if ((size_t)l * piece >= count) break;
+            DG_CUDA(cudaStreamWaitEvent(c->side, c->ev_lane[l], 0));
+        }
+        return DG_OK;
+    }
+    DG_CUDA(cudaMemcpyAsync(dst, src, count * sizeof(float), cudaMemcpyDeviceToDevice, c->side));
+    return DG_OK;
+}
+
+}  // namespace
+
+extern "C" int dg_comm_peer_alloc(dg_comm* c, int64_t floats, char host_handles_out[128])
+{
+    if (!c || !host_handles_out) return DG_ERR_NULL;
+    if (floats <= 0) return DG_ERR_DIMS;
+    if (!c->peer_ptr.empty()) return DG_ERR_STATE;                // peers still mapped: dg_comm_peer_close first
+    DeviceGuard guard(c->device);
+    DG_CUDA(cudaStreamSynchronize(c->side));
+    for (int b = 0; b < 2; ++b) {
+        if (c->peer_send[b]) DG_CUDA(cudaFree(c->peer_send[b]));
+        c->peer_send[b] = nullptr;
+    }
+    c->peer_floats = 0;
+    if (!c->peer_token) {
+        DG_CUDA(cudaMalloc(&c->peer_token, sizeof(float)));
+        DG_CUDA(cudaMemset(c->peer_token, 0, sizeof(float)));
+        DG_CUDA(cudaEventCreateWithFlags(&c->ev_barrier, cudaEventDisableTiming));
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "a CUDA IPC memory handle is expected to be 64 bytes");
+    for (int b = 0; b < 2; ++b) {
+        DG_CUDA(cudaMalloc(&c->peer_send[b], (size_t)floats * sizeof(float)));
+        cudaIpcMemHandle_t h;
+        DG_CUDA(cudaIpcGetMemHandle(&h, c->peer_send[b]));
+        memcpy(host_handles_out + 64 * b, &h, 64);
+    }
+    c->peer_floats = floats;
+    c->peer_loops = 0;
+    return DG_OK;
+}
+
+extern "C" int dg_comm_peer_open(dg_comm* c, const char* host_handles_all)
+{
+    if (!c || !host_handles_all) return DG_ERR_NULL;
+    if (!c->peer_send[0] || !c->peer_ptr.empty()) return DG_ERR_STATE;
+    DeviceGuard guard(c->device);
+    c->peer_ptr.assign(2 * (size_t)c->nranks, nullptr);
+    for (int r = 0; r < c->nranks; ++r) {
+        for (int b = 0; b < 2; ++b) {
+            if (r == c->rank) {
+                c->peer_ptr[2 * r + b] = c->peer_send[b];
+                continue;
+            }
+            cudaIpcMemHandle_t h;
+            memcpy(&h, host_handles_all + 128 * (size_t)r + 64 * b, 64);
+            void* p = nullptr;
+            cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+            if (e != cudaSuccess) {
+                peer_release(c);
+                return (int)e;
+            }
+            c->peer_ptr[2 * r + b] = static_cast<float*>(p);
+        }
+    }
+    return DG_OK;
+}
+
+extern "C" int dg_comm_peer_close(dg_comm* c)
+{
+    if (!c) return DG_ERR_NULL;
+    DeviceGuard guard(c->device);
+    DG_CUDA(cudaStreamSynchronize(c->side));
+    return peer_release(c);
+}
+
+extern "C" int64_t dg_comm_peer_capacity(const dg_comm* c)
+{
+    return c && !c->peer_ptr.empty() ? c->peer_floats : 0;
+}
+
+// Called by dg_comm_destroy.
+int dg_comm_peer_destroy(dg_comm* c)
+{
+    peer_release(c);
+    for (int b = 0; b < 2; ++b) {
+        if (c->peer_send[b]) cudaFree(c->peer_send[b]);
+        c->peer_send[b] = nullptr;
+    }
+    for (cudaStream_t st : c->peer_lanes) {
+        cudaStreamSynchronize(st);
+        cudaStreamDestroy(st);
+    }
+    c->peer_lanes.clear();
+    for (cudaEvent_t e : c->ev_lane) cudaEventDestroy(e);
+    c->ev_lane.clear();
+    if (c->peer_token) {
+        cudaFree(c->peer_token);
+        cudaEventDestroy(c->ev_barrier);
+        c->peer_token = nullptr;
+    }
+    return DG_OK;
+}
+
+extern "C" int dg_peer_spmm(dg_comm* comm, dg_comm* row_comm, int32_t n_stages, const int32_t* roots, float* const* landing,
+                            int32_t n_products, const dg_plan* const* plans, const float* const* vals,
+                            const float* const* operands, const int32_t* last_stage, const float* x_local, int32_t n,
+                            int32_t F, float* z, int timed, void* compute_stream)
+{
+    cudaStream_t compute = (cudaStream_t)compute_stream;
+    if (!comm) return DG_ERR_NULL;
+    if (n_stages < 0 || n_products < 0 || n < 0 || F < 0) return DG_ERR_DIMS;
+    if ((n_stages > 0 && (!roots || !landing)) || (n_products > 0 && (!plans || !vals || !operands || !last_stage))) return DG_ERR_NULL;
+    const size_t count = (size_t)n * (size_t)F;
+    if (count && (!x_local || !z)) return DG_ERR_NULL;
+    if (comm->peer_ptr.empty()) return DG_ERR_STATE;              // dg_comm_peer_alloc / _open come first
+    if ((int64_t)count > comm->peer_floats) return DG_ERR_SCRATCH;
+    for (int s = 0; s < n_stages; ++s) {
+        if (roots[s] < 0 || roots[s] >= comm->nranks) return DG_ERR_DIMS;
+        if (count && roots[s] != comm->rank && !landing[s]) return DG_ERR_NULL;
+    }
+    int prev = -1;
+    for (int p = 0; p < n_products; ++p) {                        // products consume the copies in the order they are issued
+        if (!plans[p] || (count && !operands[p])) return DG_ERR_NULL;
+        if (plans[p]->m != n || last_stage[p] >= n_stages || (last_stage[p] >= 0 && last_stage[p] < prev)) return DG_ERR_DIMS;
+        if (last_stage[p] > prev) prev = last_stage[p];
+    }
+    int rc;
+    DeviceGuard guard(comm->device);
+    if ((rc = make_events(comm->ev_arrived, (size_t)n_products, cudaEventDisableTiming))) return rc;
+    comm->timed_stages = 0;
+    if (timed) {
+        if ((rc = make_events(comm->t_comm, 2 * (size_t)n_products, cudaEventDefault))) return rc;
+        if ((rc = make_events(comm->t_spmm, 2 * (size_t)n_products, cudaEventDefault))) return rc;
+        DG_CUDA(cudaEventRecord(comm->t_begin, compute));
+    }
+    if (n_products == 0 && count) DG_CUDA(cudaMemsetAsync(z, 0, count * sizeof(float), compute));
+    const int b = (int)(comm->peer_loops & 1);
+    comm->peer_loops++;
+    // this rank's block goes where its peers can read it; everything queued so far on the compute stream comes first
+    if (count) DG_CUDA(cudaMemcpyAsync(comm->peer_send[b], x_local, count * sizeof(float), cudaMemcpyDeviceToDevice, compute));
+    DG_CUDA(cudaEventRecord(comm->ev_input, compute));
+    DG_CUDA(cudaStreamWaitEvent(comm->side, comm->ev_input, 0));
+    DG_NCCL(ncclAllReduce(comm->peer_token, comm->peer_token, 1, ncclFloat, ncclMax, comm->comm, comm->side));
+    DG_CUDA(cudaEventRecord(comm->ev_barrier, comm->side));
+    static const int lanes_env = [] { const char* v = getenv("DG_PEER_LANES"); return v ? atoi(v) : 0; }();
+    const int lanes = lanes_env > 0 ? (lanes_env > 8 ? 8 : lanes_env) : 2;
+    int issued = 0;                                               // copies of stages [0, issued) are on the side stream
+    for (int p = 0; p < n_products; ++p) {
+        if (timed) DG_CUDA(cudaEventRecord(comm->t_comm[2 * p], comm->side));
+        for (; issued <= last_stage[p]; ++issued) {
+            const int s = issued;
+            if (!count || roots[s] == comm->rank) {
+                if (count && landing[s])                          // the caller wants its own block inside the landing area too
+                    DG_CUDA(cudaMemcpyAsync(landing[s], x_local, count * sizeof(float), cudaMemcpyDeviceToDevice, comm->side));
+                continue;
+            }
+            if ((rc = pull_block(comm, landing[s], comm->peer_ptr[2 * roots[s] + b], count, lanes))) return rc;
+        }
+        if (timed) DG_CUDA(cudaEventRecord(comm->t_comm[2 * p + 1], comm->side));
+        if (last_stage[p] >= 0) {
+            DG_CUDA(cudaEventRecord(comm->ev_arrived[p], comm->side));
+            DG_CUDA(cudaStreamWaitEvent(compute, comm->ev_arrived[p], 0));
+        }
+        if (timed) DG_CUDA(cudaEventRecord(comm->t_spmm[2 * p], compute));
+        rc = dg_spmm_csr(plans[p], vals[p], operands[p], F, z, F, F, 1.f, p ? 1.f : 0.f, 0u, nullptr, nullptr, compute);
+        if (rc) return rc;
+        if (timed) DG_CUDA(cudaEventRecord(comm->t_spmm[2 * p + 1], compute));
+    }
+    // later work on the compute stream (the next product's copy into the other send buffer included) is ordered after
+    // this product's meeting point even on a rank that read nothing remote
+    DG_CUDA(cudaStreamWaitEvent(compute, comm->ev_barrier, 0));
+    if (row_comm) {
+        rc = dg_comm_allreduce_sum(row_comm, z, (int64_t)n * F, compute_stream);
+        if (rc) return rc;
+    }
+    if (timed) {
+        DG_CUDA(cudaEventRecord(comm->t_end, compute));
+        comm->timed_stages = n_products;
+    }
+    return DG_OK;
+}

@@ -12,37 +12,9 @@
 #include <new>
 #include <vector>
 #include "dg_internal.h"
-
-#define DG_NCCL(expr)                                                  \
-    do {                                                               \
-        ncclResult_t _r = (expr);                                      \
-        if (_r != ncclSuccess) return DG_NCCL_ERROR_BASE + (int)_r;    \
-    } while (0)
-
-struct dg_comm {
-    ncclComm_t comm;
-    int rank, nranks, device;
-    cudaStream_t side;                       // broadcasts run here
-    cudaEvent_t ev_input;                    // this rank's block is ready on the compute stream
-    std::vector<cudaEvent_t> ev_arrived;     // per receive buffer: broadcast into it finished
-    std::vector<cudaEvent_t> ev_free;        // per receive buffer: the product that read it finished
-    std::vector<cudaEvent_t> ev_packed;      // per pack buffer: the column chunk to send is ready
-    std::vector<cudaEvent_t> t_comm, t_spmm; // timing pairs per stage (2 events each)
-    cudaEvent_t t_begin, t_end;
-    int timed_stages;
-};
+#include "dg_comm.h"
 
 namespace {
-
-int make_events(std::vector<cudaEvent_t>& v, size_t count, unsigned flags)
-{
-    while (v.size() < count) {
-        cudaEvent_t e;
-        DG_CUDA(cudaEventCreateWithFlags(&e, flags));
-        v.push_back(e);
-    }
-    return DG_OK;
-}
 
 int finish_comm(ncclComm_t nc, dg_comm** out)
 {
@@ -62,12 +34,6 @@ int finish_comm(ncclComm_t nc, dg_comm** out)
     *out = c;
     return DG_OK;
 }
-
-struct DeviceGuard {
-    int prev = -1;
-    explicit DeviceGuard(int dev) { cudaGetDevice(&prev); if (prev != dev) cudaSetDevice(dev); else prev = -1; }
-    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
-};
 
 // `group` consecutive stages share one product: plans[g] is n x (stages_in_group * n).
 int check_loop_args(int32_t n_stages, const int32_t* roots, int32_t group, const dg_plan* const* plans,
@@ -197,6 +163,7 @@ extern "C" int dg_comm_destroy(dg_comm* c)
     if (!c) return DG_OK;
     DeviceGuard guard(c->device);
     cudaStreamSynchronize(c->side);
+    dg_comm_peer_destroy(c);
     ncclCommDestroy(c->comm);
     for (auto* v : {&c->ev_arrived, &c->ev_free, &c->ev_packed, &c->t_comm, &c->t_spmm})
         for (cudaEvent_t e : *v) cudaEventDestroy(e);

@@ -46,7 +46,8 @@ class DistEnv:
         # 'local_first': own block first, one receive area for all remote blocks, every broadcast queued up front
         self.stage_order = stage_order if stage_order is not None else os.environ.get('DIST_GNN_STAGE_ORDER', 'reference')
         # 'feature_chunks' (1D): all-gather the operand one column chunk at a time, one full-row product per chunk
-        if self.stage_order not in ('reference', 'local_first', 'feature_chunks'):
+        # 'peer_copy': own block first, remote blocks pulled from their owners' send buffers by device-to-device copies
+        if self.stage_order not in ('reference', 'local_first', 'feature_chunks', 'peer_copy'):
             raise ValueError(f'unknown stage order {self.stage_order!r}')
         self.chunk_width = int(os.environ.get('DIST_GNN_CHUNK_WIDTH', 64))
         DistEnv.env = self
@@ -134,8 +135,33 @@ class DistEnv:
             self._recv[(tag, nbuf)] = bufs
         return [b[:need].view(n, F) for b in bufs]
 
+    def ensure_peer_buffers(self, floats):
+        """Send buffers of the 'peer_copy' stage order, mapped by every rank of the column communicator.  Collective
+        over that communicator: every rank asks for the same sizes in the same order (they run the same model), so
+        they all grow at the same call."""
+        comm = self.col_comm
+        if comm.peer_capacity() >= floats:
+            return
+        group = self.world_group if self.rep == 1 else self.col_groups[self.rank_col]
+        torch.cuda.synchronize(self.device)
+        if comm.peer_capacity() > 0:
+            comm.peer_close()
+            dist.barrier(group, device_ids=[self.device.index])     # nobody frees a buffer a peer still maps
+        mine = comm.peer_alloc(floats)
+        handles = [None] * comm.size
+        dist.all_gather_object(handles, mine, group=group)
+        comm.peer_open(handles)
+        dist.barrier(group, device_ids=[self.device.index])
+
     def shutdown(self):
-        for c in {id(c): c for c in (self.row_comm, self.col_comm, self.comm) if c is not None}.values():
+        comms = list({id(c): c for c in (self.row_comm, self.col_comm, self.comm) if c is not None}.values())
+        if any(c.peer_capacity() > 0 for c in comms):
+            torch.cuda.synchronize(self.device)
+            for c in comms:
+                if c.peer_capacity() > 0:
+                    c.peer_close()
+            self.barrier_all()                                      # every mapping is gone before any owner frees its buffers
+        for c in comms:
             c.destroy()
         self.comm = self.col_comm = self.row_comm = None
         if dist.is_initialized():

@@ -126,6 +126,11 @@ def _stage_loop(env, local_adj_parts, x, z, stages, comm):
         with env.timer.timing_cuda('broadcast+spmm'):
             spmm_cpp.allgather_spmm(comm, plan, x, pack, area, z, widths)
         return z
+    if comm is not None and env.stage_order == 'peer_copy':
+        env.ensure_peer_buffers(n * width)
+        with env.timer.timing_cuda('broadcast+spmm'):
+            spmm_cpp.peer_spmm(comm, *ordered_products(env, local_adj_parts, stages, x, rotate=True), x, z, row_comm=env.row_comm)
+        return z
     if comm is not None and env.stage_order == 'local_first':
         with env.timer.timing_cuda('broadcast+spmm'):
             spmm_cpp.bcast_spmm_ordered(comm, *ordered_products(env, local_adj_parts, stages, x), x, z,
@@ -139,25 +144,32 @@ def _stage_loop(env, local_adj_parts, x, z, stages, comm):
     return z
 
 
-def ordered_products(env, adj_parts, stages, x):
-    """Arguments (roots, landing, products) of spmm_cpp.bcast_spmm_ordered for the 'local_first' stage order: the block
-    this rank roots is multiplied first, straight from x; the remote blocks land side by side in one receive area,
-    in broadcast order, and are multiplied env.stage_group at a time as they arrive."""
-    me = env.col_comm.rank
+def ordered_products(env, adj_parts, stages, x, rotate=False):
+    """Arguments (roots, landing, products) of spmm_cpp.bcast_spmm_ordered / peer_spmm for the stage orders that multiply
+    this rank's own block first, straight from x: the remote blocks land side by side in one receive area, in transfer
+    order, and are multiplied env.stage_group at a time as they arrive.
+    rotate=False: transfers in schedule order, the same on every rank (collective broadcasts need that).
+    rotate=True:  each rank lists its own stages first and then the remote ones starting with the rank after itself, so
+                  that at any moment every send buffer serves one reader (peer copies need no common order)."""
+    me, size = env.col_comm.rank, env.col_comm.size
     n, width = x.shape
     remote = [i for i, st in enumerate(stages) if st.root_in_group != me]
     own = [i for i, st in enumerate(stages) if st.root_in_group == me]
+    if rotate:
+        remote.sort(key=lambda i: ((stages[i].root_in_group - me) % size, i))
     area = env.recv_buffers(max(len(remote), 1) * n, width, nbuf=1)[0]
+    issue = own + remote if rotate else list(range(len(stages)))        # the order the transfers are listed in
+    position = {i: pos for pos, i in enumerate(issue)}
     landing = [None] * len(stages)
     for pos, i in enumerate(remote):
-        landing[i] = area[pos * n:(pos + 1) * n]
+        landing[position[i]] = area[pos * n:(pos + 1) * n]
     products = [(spmm_cpp.plan_for(adj_parts[stages[i].part]), x, -1) for i in own]
     group = max(1, min(env.stage_group, len(remote)))
     plans = group_plans(adj_parts, [stages[i].part for i in remote], group) if remote else []
     for g, plan in enumerate(plans):
         members = remote[g * group:(g + 1) * group]
-        products.append((plan, area[g * group * n:(g * group + len(members)) * n], members[-1]))
-    return [st.root_in_group for st in stages], landing, products
+        products.append((plan, area[g * group * n:(g * group + len(members)) * n], max(position[i] for i in members)))
+    return [stages[i].root_in_group for i in issue], landing, products
 
 
 _group_plan_cache = {}

@@ -73,6 +73,11 @@ def lib():
             'dg_allgather_spmm': ([vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp, ctypes.c_int, vp], ctypes.c_int),
             'dg_comm_last_times': ([vp, ctypes.POINTER(StageTimes)], ctypes.c_int),
             'dg_select_kernel': ([ctypes.c_int], ctypes.c_int),
+            'dg_comm_peer_alloc': ([vp, i64, ctypes.c_char_p], ctypes.c_int),
+            'dg_comm_peer_open': ([vp, ctypes.c_char_p], ctypes.c_int),
+            'dg_comm_peer_close': ([vp], ctypes.c_int),
+            'dg_comm_peer_capacity': ([vp], ctypes.c_int64),
+            'dg_peer_spmm': ([vp, vp, i32, vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, vp, ctypes.c_int, vp], ctypes.c_int),
             'dg_dense_split': ([vp, vp, vp, i64, vp], ctypes.c_int),
             'dg_dense_supported': ([i64, i32, i32, i64, i64, vp, vp, vp], ctypes.c_int),
             'dg_dense_nt': ([vp, i64, vp, vp, i64, vp, i64, i64, i32, i32, i32, vp], ctypes.c_int),
@@ -291,6 +296,28 @@ class Comm:
             check(lib().dg_comm_last_times(self.handle, ctypes.byref(s)))
         return dict(comm_ms=s.comm_ms, spmm_ms=s.spmm_ms, total_ms=s.total_ms, stages=s.stages)
 
+    def peer_alloc(self, floats):
+        """Allocates this rank's two send buffers of the peer-copy loop; returns their CUDA IPC handles (128 bytes)."""
+        buf = ctypes.create_string_buffer(128)
+        with torch.cuda.device(self.device):
+            check(lib().dg_comm_peer_alloc(self.handle, int(floats), buf))
+        return buf.raw
+
+    def peer_open(self, handles):
+        """Maps every rank's send buffers; handles: the peer_alloc results of all ranks in communicator rank order."""
+        blob = b''.join(handles)
+        if len(blob) != 128 * self.size:
+            raise RuntimeError(f'expected {self.size} handle records of 128 bytes')
+        with torch.cuda.device(self.device):
+            check(lib().dg_comm_peer_open(self.handle, blob))
+
+    def peer_close(self):
+        with torch.cuda.device(self.device):
+            check(lib().dg_comm_peer_close(self.handle))
+
+    def peer_capacity(self):
+        return int(lib().dg_comm_peer_capacity(self.handle))
+
     def destroy(self):
         h, self.handle = self.handle, None
         if h and _lib is not None:
@@ -325,7 +352,7 @@ def bcast_spmm(comm, roots, plans, x_local, recv, z, row_comm=None, timed=False,
     return z
 
 
-def bcast_spmm_ordered(comm, roots, landing, products, x_local, z, row_comm=None, timed=False, bcast_group=1):
+def bcast_spmm_ordered(comm, roots, landing, products, x_local, z, row_comm=None, timed=False, bcast_group=1, peer_copies=False):
     """dg_bcast_spmm_ordered: every broadcast queued up front, products in the given order.
 
     roots[s]     root (rank inside comm) of broadcast s; the same list on every rank
@@ -346,9 +373,20 @@ def bcast_spmm_ordered(comm, roots, landing, products, x_local, z, row_comm=None
     op_arr = (ctypes.c_void_p * max(P, 1))(*[t.data_ptr() for _, t, _ in products])
     last_arr = (ctypes.c_int32 * max(P, 1))(*[l for _, _, l in products])
     with torch.cuda.device(x_local.device):
-        check(lib().dg_bcast_spmm_ordered(comm.handle, row_comm.handle if row_comm else None, S, roots_arr, bcast_group, land_arr, P, plan_arr,
-                                          val_arr, op_arr, last_arr, x_local.data_ptr(), n, F, z.data_ptr(), int(timed), _stream()))
+        if peer_copies:
+            check(lib().dg_peer_spmm(comm.handle, row_comm.handle if row_comm else None, S, roots_arr, land_arr, P, plan_arr,
+                                     val_arr, op_arr, last_arr, x_local.data_ptr(), n, F, z.data_ptr(), int(timed), _stream()))
+        else:
+            check(lib().dg_bcast_spmm_ordered(comm.handle, row_comm.handle if row_comm else None, S, roots_arr, bcast_group, land_arr, P,
+                                              plan_arr, val_arr, op_arr, last_arr, x_local.data_ptr(), n, F, z.data_ptr(), int(timed),
+                                              _stream()))
     return z
+
+
+def peer_spmm(comm, roots, landing, products, x_local, z, row_comm=None, timed=False):
+    """dg_peer_spmm: the arguments of bcast_spmm_ordered, but every remote block is pulled from its root's send buffer
+    by a device-to-device copy (Comm.peer_alloc / peer_open come first) and the stage order may differ per rank."""
+    return bcast_spmm_ordered(comm, roots, landing, products, x_local, z, row_comm=row_comm, timed=timed, peer_copies=True)
 
 
 def chunk_widths(F, target=64):

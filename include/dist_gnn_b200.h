@@ -172,6 +172,29 @@ int dg_bcast_spmm_ordered(dg_comm* comm, dg_comm* row_comm, int32_t n_stages, co
                           const float* const* host_vals, const float* const* host_operands,
                           const int32_t* host_last_stage, const float* x_local, int32_t n, int32_t F, float* z,
                           int timed, void* compute_stream);
+/* ---- the same distributed product with the remote blocks pulled by the copy engines (no counterpart in the reference;
+ * replaces gcn.py:16-30 / dist_15d.py:61-106 like dg_bcast_spmm_ordered) ---------------------------------------------
+ * Set-up, once per communicator and buffer size (collective in the sense that every rank must do it):
+ *   dg_comm_peer_alloc   allocates this rank's two send buffers of `floats` floats each and writes their two 64-byte
+ *                        CUDA IPC handles to host_handles_out (128 bytes);
+ *   (the host exchanges the handles, e.g. with an all-gather of bytes)
+ *   dg_comm_peer_open    maps every rank's buffers; host_handles_all holds nranks x 128 bytes in communicator rank order;
+ *   dg_comm_peer_close   unmaps them again (before the owners free theirs: close on all ranks, meet, then destroy).
+ * dg_peer_spmm has the arguments of dg_bcast_spmm_ordered without bcast_group.  It copies x_local into this rank's send
+ * buffer, meets the other ranks in a one-float all-reduce on the side stream, and then issues one device-to-device
+ * copy per remote stage - from the root's send buffer into host_landing[s] - in the order of host_roots; a stage this
+ * rank roots is read from x_local (host_landing[s] == NULL) or copied locally.  Different ranks may list different
+ * stages in different orders (each typically starts with the rank after itself, so that no buffer serves two readers at
+ * once); the only call every rank of the communicator must make is dg_peer_spmm itself, once per distributed product.
+ * DG_ERR_STATE before the set-up, DG_ERR_SCRATCH when n * F exceeds the send buffers. */
+int dg_comm_peer_alloc(dg_comm* comm, int64_t floats, char host_handles_out[128]);
+int dg_comm_peer_open(dg_comm* comm, const char* host_handles_all);
+int dg_comm_peer_close(dg_comm* comm);
+int64_t dg_comm_peer_capacity(const dg_comm* comm);
+int dg_peer_spmm(dg_comm* comm, dg_comm* row_comm, int32_t n_stages, const int32_t* host_roots, float* const* host_landing,
+                 int32_t n_products, const dg_plan* const* host_plans, const float* const* host_vals,
+                 const float* const* host_operands, const int32_t* host_last_stage, const float* x_local, int32_t n,
+                 int32_t F, float* z, int timed, void* compute_stream);
 /* 1D only: the same distributed product pipelined along the feature dimension (replaces gcn.py:16-30 as a whole).  The
  * n x F operand is cut into n_chunks column chunks (host_chunk_widths, summing to F).  Chunk c of every rank is
  * all-gathered on the side stream into host_area[c % 2] ((nranks*n) x w_c, rank r's rows at r*n) while the compute

@@ -60,7 +60,11 @@ def _worker(rank, world, rep, port, out_dir, mode):
                 rec[f'zlg{i}'] = broadcast(g.adj_parts, x, f'w{width}').cpu().numpy()
                 env.stage_group, env.stage_order, env.chunk_width = 1, 'feature_chunks', 16     # 1D only; 1.5D falls through
                 rec[f'zf{i}'] = broadcast(g.adj_parts, x, f'w{width}').cpu().numpy()
-                env.stage_order, env.chunk_width = 'reference', 64
+                env.stage_order, env.chunk_width = 'peer_copy', 64      # remote blocks pulled from the owners' send buffers
+                rec[f'zp{i}'] = broadcast(g.adj_parts, x, f'w{width}').cpu().numpy()
+                env.stage_group = 2
+                rec[f'zpg{i}'] = broadcast(g.adj_parts, x, f'w{width}').cpu().numpy()
+                env.stage_group, env.stage_order = 1, 'reference'
         torch.cuda.synchronize()
         np.savez(os.path.join(out_dir, f'rank{rank}.npz'), **rec)
     finally:
@@ -104,7 +108,7 @@ def test_back_to_back_stage_loops_at_two_ranks(golden):
         want = ref_gcn.broadcast_1d([p['adj_parts'] for p in parts], [res[r][f'x{i}'] for r in range(2)])
         for r in range(2):
             assert_close(res[r][f'z{i}'], want[r], 1e-5, f'loop {i} rank {r}')
-            for key in ('zg', 'zl', 'zlg', 'zf'):
+            for key in ('zg', 'zl', 'zlg', 'zf', 'zp', 'zpg'):
                 assert_close(res[r][f'{key}{i}'], want[r], 1e-5, f'{key} loop {i} rank {r}')
 
 
@@ -117,5 +121,5 @@ def test_15d_stage_loop_at_four_ranks(golden):
         want = ref_gcn.broadcast_15d([p['adj_parts'] for p in parts], [res[b * 2][f'x{i}'] for b in range(2)], 4, 2)
         for r in range(4):
             assert_close(res[r][f'z{i}'], want[r], 1e-5, f'loop {i} rank {r}')
-            for key in ('zg', 'zl', 'zlg', 'zf'):
+            for key in ('zg', 'zl', 'zlg', 'zf', 'zp', 'zpg'):
                 assert_close(res[r][f'{key}{i}'], want[r], 1e-5, f'{key} loop {i} rank {r}')
