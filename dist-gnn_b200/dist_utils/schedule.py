@@ -49,3 +49,14 @@ def stages_15d(rank, world_size, rep):
 
 def stages(rank, world_size, rep=1):
     return stages_1d(world_size) if rep == 1 else stages_15d(rank, world_size, rep)
+
+
+def pull_order(stage_list, me, size):
+    """Order in which a rank of a `size`-rank communicator handles its stages when remote blocks are pulled from their
+    owners (stage order 'peer_copy'): (own, remote) index lists into stage_list - the stages this rank roots itself, then
+    the remote ones sorted by the distance of their root after this rank, so that in step j of a 1D loop every rank reads
+    from rank me + j and no owner serves two readers at once."""
+    own = [i for i, st in enumerate(stage_list) if st.root_in_group == me]
+    remote = [i for i, st in enumerate(stage_list) if st.root_in_group != me]
+    remote.sort(key=lambda i: ((stage_list[i].root_in_group - me) % size, i))
+    return own, remote

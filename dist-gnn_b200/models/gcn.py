@@ -16,7 +16,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 import spmm_cpp
-from dist_utils import DistEnv
+from dist_utils import DistEnv, schedule
 
 
 def spmm(A, B, C):
@@ -153,10 +153,11 @@ def ordered_products(env, adj_parts, stages, x, rotate=False):
                   that at any moment every send buffer serves one reader (peer copies need no common order)."""
     me, size = env.col_comm.rank, env.col_comm.size
     n, width = x.shape
-    remote = [i for i, st in enumerate(stages) if st.root_in_group != me]
-    own = [i for i, st in enumerate(stages) if st.root_in_group == me]
     if rotate:
-        remote.sort(key=lambda i: ((stages[i].root_in_group - me) % size, i))
+        own, remote = schedule.pull_order(stages, me, size)
+    else:
+        remote = [i for i, st in enumerate(stages) if st.root_in_group != me]
+        own = [i for i, st in enumerate(stages) if st.root_in_group == me]
     area = env.recv_buffers(max(len(remote), 1) * n, width, nbuf=1)[0]
     issue = own + remote if rotate else list(range(len(stages)))        # the order the transfers are listed in
     position = {i: pos for pos, i in enumerate(issue)}

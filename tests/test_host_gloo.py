@@ -139,3 +139,26 @@ def test_schedule_shapes():
         schedule.check_layout(6, 4)
     with pytest.raises(ValueError):
         schedule.check_layout(2, 2)
+
+
+def test_pull_order_of_the_peer_copy_loop():
+    """1D: every rank handles its own block first and then reads from rank+1, rank+2, ...: at every step the P readers
+    read from P different owners.  1.5D: own stages first, every stage exactly once."""
+    from dist_utils import schedule
+    for P in (2, 3, 8):
+        orders = []
+        for me in range(P):
+            st = schedule.stages(me, P, 1)
+            own, remote = schedule.pull_order(st, me, P)
+            assert [st[i].root_in_group for i in own] == [me]
+            assert [st[i].root_in_group for i in remote] == [(me + j) % P for j in range(1, P)]
+            orders.append([st[i].root_in_group for i in remote])
+        for step in range(P - 1):
+            assert sorted(o[step] for o in orders) == list(range(P))
+    for P, c in ((8, 2), (12, 3), (4, 2)):
+        for rank in range(P):
+            st = schedule.stages(rank, P, c)
+            me = schedule.col_groups(P, c)[rank % c].index(rank)
+            own, remote = schedule.pull_order(st, me, P // c)
+            assert sorted(own + remote) == list(range(len(st)))
+            assert all(st[i].root_in_group == me for i in own) and all(st[i].root_in_group != me for i in remote)
