@@ -16,6 +16,7 @@
 // Every mbarrier wait is bounded; a role that gives up sets the status word and the CTA still frees its TMEM.
 #include <cuda.h>
 #include <cstdint>
+#include <cstring>
 #include "dg_internal.h"
 
 namespace {
@@ -267,6 +268,180 @@ k_dense_nt(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
 }
 
+// The same product with one CTA per SM walking over the row tiles (tile, tile + grid, ...): two accumulators in tensor
+// memory (columns 0 and 256) and separate warps for the operand split and for the epilogue, so that tile t is read out
+// of tensor memory and stored while tile t+1 is already being loaded, split and multiplied.
+// Warps: 0 TMA, 1 MMA issue + tensor-memory allocation, 2-5 split A, 6-9 epilogue (warp w reads lane quarter w % 4).
+constexpr int kThreadsPersistent = 320;
+
+__global__ void __launch_bounds__(kThreadsPersistent, 1)
+k_dense_nt_persistent(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmBh,
+                      const __grid_constant__ CUtensorMap tmBt, const DenseArgs a, const int n_tiles)
+{
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    unsigned char* gbase = smem_raw + (base - raw);
+    const int b_bytes = a.n_pad * 128;
+    const int stage_bytes = 2 * BM * 128 + 2 * b_bytes;
+    const uint32_t bars = base + STAGES * stage_bytes;
+    const uint32_t full0 = bars, ready0 = bars + 8 * STAGES, empty0 = bars + 16 * STAGES;
+    const uint32_t acc_full0 = bars + 24 * STAGES, acc_empty0 = acc_full0 + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + STAGES * stage_bytes + 24 * STAGES + 32);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nslabs = (a.K + BK - 1) / BK;
+    constexpr int kTmemCols = 512;                                // two accumulators of up to 256 columns
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(ready0 + 8 * s, 128);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full0 + 8 * b, 1);
+            mbar_init(acc_empty0 + 8 * b, 128);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {                                          // TMA producer: one ring of stages across all tiles
+            int it = 0;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                for (int i = 0; i < nslabs; ++i, ++it) {
+                    const int s = it % STAGES, u = it / STAGES;
+                    if (u > 0) ok = mbar_wait(empty0 + 8 * s, (u - 1) & 1);
+                    if (!ok) break;
+                    const uint32_t st = base + s * stage_bytes;
+                    mbar_expect_tx(full0 + 8 * s, BM * 128 + 2 * b_bytes);
+                    tma_load_2d(st, &tmA, i * BK, tile * BM, full0 + 8 * s);
+                    tma_load_2d(st + 2 * BM * 128, &tmBh, i * BK, 0, full0 + 8 * s);
+                    tma_load_2d(st + 2 * BM * 128 + b_bytes, &tmBt, i * BK, 0, full0 + 8 * s);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {                                          // MMA issuer
+            const uint32_t idesc = umma_idesc_tf32(a.n_pad);
+            int it = 0, lt = 0;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++lt) {
+                const int b = lt & 1, v = lt >> 1;
+                if (lt >= 2) ok = mbar_wait(acc_empty0 + 8 * b, (v - 1) & 1);     // the epilogue has drained this accumulator
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t acc = tmem + (uint32_t)(b * 256);
+                for (int i = 0; i < nslabs; ++i, ++it) {
+                    const int s = it % STAGES, u = it / STAGES;
+                    ok = mbar_wait(ready0 + 8 * s, u & 1);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t st = base + s * stage_bytes;
+                    const uint64_t a_head = umma_desc_sw128(st), a_tail = umma_desc_sw128(st + BM * 128);
+                    const uint64_t b_head = umma_desc_sw128(st + 2 * BM * 128), b_tail = umma_desc_sw128(st + 2 * BM * 128 + b_bytes);
+#pragma unroll
+                    for (int k = 0; k < BK / 8; ++k) {
+                        umma_tf32(acc, a_tail + 2 * k, b_head + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                        umma_tf32(acc, a_head + 2 * k, b_tail + 2 * k, idesc, 1u);
+                        umma_tf32(acc, a_head + 2 * k, b_head + 2 * k, idesc, 1u);
+                    }
+                    umma_commit(empty0 + 8 * s);
+                }
+                if (ok) umma_commit(acc_full0 + 8 * b);
+            }
+        }
+    } else if (warp < 6) {
+        const int t = threadIdx.x - 64;                           // 0..127: split the A slab of every stage
+        int it = 0;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            for (int i = 0; i < nslabs; ++i, ++it) {
+                const int s = it % STAGES, u = it / STAGES;
+                ok = mbar_wait(full0 + 8 * s, u & 1);
+                if (!ok) break;
+                float4* head = reinterpret_cast<float4*>(gbase + (size_t)s * stage_bytes);
+                float4* tail = head + BM * 128 / 16;
+#pragma unroll 4
+                for (int j = t; j < BM * 128 / 16; j += 128) {
+                    const float4 x = head[j];
+                    float4 h;
+                    h.x = __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u); h.y = __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
+                    h.z = __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u); h.w = __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
+                    head[j] = h;
+                    tail[j] = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(ready0 + 8 * s);
+            }
+        }
+    } else {
+        const int q = warp & 3;                                   // a warp may only read its own quarter of the TMEM lanes
+        const bool vec_ok = (a.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.C) & 15) == 0);
+        const bool mvec_ok = a.mask && (a.ldm % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.mask) & 15) == 0);
+        int lt = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++lt) {
+            const int b = lt & 1, v = lt >> 1;
+            ok = __all_sync(0xffffffffu, mbar_wait(acc_full0 + 8 * b, v & 1));     // tcgen05.ld is warp-collective
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int64_t row = (int64_t)tile * BM + q * 32 + lane;
+            float* crow = a.C + row * a.ldc;
+            const float* mrow = a.mask ? a.mask + row * a.ldm : nullptr;
+            for (int c0 = 0; c0 < a.n_pad; c0 += 16) {
+                float mk[16];
+                if (mrow && row < a.M) {
+                    if (mvec_ok && c0 + 16 <= a.N) {
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4) {
+                            const float4 m4 = __ldg(reinterpret_cast<const float4*>(mrow + c0 + j));
+                            mk[j] = m4.x; mk[j + 1] = m4.y; mk[j + 2] = m4.z; mk[j + 3] = m4.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) mk[j] = c0 + j < a.N ? __ldg(mrow + c0 + j) : 0.f;
+                    }
+                }
+                uint32_t r[16];
+                tmem_ld16(tmem + (uint32_t)(b * 256) + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row < a.M) {
+                    float v16[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        v16[j] = __uint_as_float(r[j]);
+                        if (a.relu) v16[j] = fmaxf(v16[j], 0.f);
+                        if (mrow && !(mk[j] > 0.f)) v16[j] = 0.f;
+                    }
+                    if (vec_ok && c0 + 16 <= a.N) {
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4)
+                            __stcs(reinterpret_cast<float4*>(crow + c0 + j), make_float4(v16[j], v16[j + 1], v16[j + 2], v16[j + 3]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (c0 + j < a.N) crow[c0 + j] = v16[j];
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(acc_empty0 + 8 * b);
+        }
+    }
+    if (!ok) atomicExch(a.status, 1);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+}
+
 __global__ void k_tf32_split(const float* __restrict__ src, float* __restrict__ head, float* __restrict__ tail, int64_t count)
 {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -367,9 +542,23 @@ extern "C" int dg_dense_nt_masked(const float* A, int64_t lda, const float* Bt_h
     if ((rc = make_map(&tmA, A, M, K, lda, BM)) || (rc = make_map(&tmBh, Bt_head, N, K, ldb, a.n_pad)) ||
         (rc = make_map(&tmBt, Bt_tail, N, K, ldb, a.n_pad)))
         return rc;
-    const size_t smem = (size_t)STAGES * (2 * BM * 128 + 2 * a.n_pad * 128) + 24 * STAGES + 16 + 1024;
-    DG_CUDA(cudaFuncSetAttribute(k_dense_nt, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    k_dense_nt<<<(unsigned)((M + BM - 1) / BM), kThreads, smem, (cudaStream_t)stream>>>(tmA, tmBh, tmBt, a);
+    const size_t smem = (size_t)STAGES * (2 * BM * 128 + 2 * a.n_pad * 128) + 24 * STAGES + 48 + 1024;
+    const int n_tiles = (int)((M + BM - 1) / BM);
+    // two kernels: one tile per CTA, or one persistent CTA per SM walking the tiles (DG_DENSE_NT=tile|persistent forces one)
+    // Narrow results leave room for two one-tile CTAs per SM, which overlap each other's load latency better than the
+    // persistent CTA's two stages do (2,449,029 x 256 -> 47: 1.09 ms against 1.28 ms; -> 256: 2.16 against 1.88).
+    static const int forced = [] { const char* v = getenv("DG_DENSE_NT"); return !v ? 0 : !strcmp(v, "tile") ? 1 : !strcmp(v, "persistent") ? 2 : 0; }();
+    const bool per_tile = forced == 1 || (forced == 0 && a.n_pad <= 128);
+    if (per_tile) {
+        DG_CUDA(cudaFuncSetAttribute(k_dense_nt, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k_dense_nt<<<(unsigned)n_tiles, kThreads, smem, (cudaStream_t)stream>>>(tmA, tmBh, tmBt, a);
+        return (int)cudaGetLastError();
+    }
+    int dev = 0, sms = 0;
+    DG_CUDA(cudaGetDevice(&dev));
+    DG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    DG_CUDA(cudaFuncSetAttribute(k_dense_nt_persistent, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    k_dense_nt_persistent<<<(unsigned)(n_tiles < sms ? n_tiles : sms), kThreadsPersistent, smem, (cudaStream_t)stream>>>(tmA, tmBh, tmBt, a, n_tiles);
     return (int)cudaGetLastError();
 }
 

@@ -214,8 +214,13 @@ def select_kernel(family):
     check(lib().dg_select_kernel({'auto': 0, 'rows': 1, 'stream': 2}.get(family, family)))
 
 
+dense_launches = 0      # kernels launched by dense_split / dense_nt / dense_tn since the last profile_begin
+
+
 def profile_begin():
     """Start bracketing every local product with CUDA events (dg_profile_begin)."""
+    global dense_launches
+    dense_launches = 0
     check(lib().dg_profile_begin())
 
 
@@ -223,7 +228,9 @@ def profile_end():
     """Synchronise and return the summed product time, traffic models, flops and kernel-launch count."""
     p = Profile()
     check(lib().dg_profile_end(ctypes.byref(p)))
-    return {name: getattr(p, name) for name, _ in Profile._fields_}
+    out = {name: getattr(p, name) for name, _ in Profile._fields_}
+    out['dense_launches'] = dense_launches
+    return out
 
 
 _plan_cache = {}
@@ -423,6 +430,8 @@ def allgather_spmm(comm, plan, x_local, pack, area, z, widths, timed=False):
 def dense_split(w):
     """TF32-exact head and residual tail of a small fp32 CUDA matrix (dg_dense_split); head + tail == w exactly."""
     _dev_tensor(w, torch.float32, 'matrix')
+    global dense_launches
+    dense_launches += 1
     head, tail = torch.empty_like(w), torch.empty_like(w)
     with torch.cuda.device(w.device):
         check(lib().dg_dense_split(w.data_ptr(), head.data_ptr(), tail.data_ptr(), w.numel(), _stream()))
@@ -449,7 +458,9 @@ def dense_nt(a, bt, relu=False, mask=None):
     ldb = bt.size(1)
     if M == 0 or not lib().dg_dense_supported(M, N, K, lda, ldb, a.data_ptr(), bt.data_ptr(), bt.data_ptr()):
         return None
+    global dense_launches
     head, tail = dense_split(bt)
+    dense_launches += 1
     c = torch.empty((M, N), dtype=torch.float32, device=a.device)
     with torch.cuda.device(a.device):
         check(lib().dg_dense_nt_masked(a.data_ptr(), lda, head.data_ptr(), tail.data_ptr(), ldb, c.data_ptr(), N, M, N, K, int(relu),
@@ -474,6 +485,8 @@ def dense_tn(x, g):
     scratch = _tn_scratch.get(x.device)
     if scratch is None:
         scratch = _tn_scratch[x.device] = torch.empty(ctas * 256 * 256, dtype=torch.float32, device=x.device)
+    global dense_launches
+    dense_launches += 2                 # the product and the reduction over the CTAs' partials
     d = torch.empty((Km, Nn), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
         check(lib().dg_dense_tn(x.data_ptr(), ldx, g.data_ptr(), ldg, d.data_ptr(), Nn, n, Km, Nn, scratch.data_ptr(), scratch.numel(),
