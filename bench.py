@@ -299,8 +299,7 @@ def measure_stage_loops(env, g, widths, spmm_cpp):
                 chunks = spmm_cpp.chunk_widths(width, env.chunk_width)
                 spmm_cpp.allgather_spmm(env.col_comm, plan, x, env.recv_buffers(n, max(chunks), tag='pack'),
                                         env.recv_buffers(n * env.col_comm.size, max(chunks), tag='area'), z, chunks, timed=timed)
-            elif env.stage_order == 'peer_copy':
-                env.ensure_peer_buffers(n * width)
+            elif env.stage_order == 'peer_copy' and env.ensure_peer_buffers(n * width):
                 spmm_cpp.peer_spmm(env.col_comm, *ordered_products(env, g.adj_parts, stages, x, rotate=True), x, z,
                                    row_comm=env.row_comm, timed=timed)
             elif env.stage_order == 'local_first':

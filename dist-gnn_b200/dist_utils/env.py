@@ -37,18 +37,27 @@ class DistEnv:
         self.timer = DistTimer(self)
         self.store = dist.PrefixStore('dist_gnn_timer', dist.distributed_c10d._get_default_store())
         self._recv = {}
-        # stages fused into one product by the CUDA stage loop (1 = stage by stage, as the reference)
-        # Default: two products per distributed SpMM (half of the stages each) - measured fastest at 4 and 8 GPUs: longer
-        # rows per product and one read-modify-write of z instead of P-1, while the second half still travels under the first.
-        chosen = stage_group if stage_group is not None else os.environ.get('DIST_GNN_STAGE_GROUP')
-        self.stage_group = max(1, int(chosen)) if chosen is not None else max(1, (len(self.stages()) + 1) // 2)
-        # 'reference': products in ascending stage order (the reference's sum order), two receive buffers;
-        # 'local_first': own block first, one receive area for all remote blocks, every broadcast queued up front
-        self.stage_order = stage_order if stage_order is not None else os.environ.get('DIST_GNN_STAGE_ORDER', 'reference')
-        # 'feature_chunks' (1D): all-gather the operand one column chunk at a time, one full-row product per chunk
-        # 'peer_copy': own block first, remote blocks pulled from their owners' send buffers by device-to-device copies
+        # Order of the products inside a distributed SpMM:
+        # 'reference':   ascending stage order (the reference's sum order), NCCL broadcasts into two receive buffers;
+        # 'local_first': own block first, one receive area for all remote blocks, every broadcast queued up front;
+        # 'feature_chunks' (1D): all-gather the operand one column chunk at a time, one full-row product per chunk;
+        # 'peer_copy':   own block first, remote blocks pulled from their owners' send buffers by device-to-device copies.
+        # Default: peer_copy for 1D (fastest at 2 and 8 GPUs: 39.9 / 25.4 ms against 48.2 / 27.4 for 'reference', with 0.8-0.9
+        # of the transfer hidden), reference for 1.5D (peer copies were slower there: 48 against 35 ms).
+        default_order = 'peer_copy' if rep == 1 else 'reference'
+        self.stage_order = stage_order if stage_order is not None else os.environ.get('DIST_GNN_STAGE_ORDER', default_order)
         if self.stage_order not in ('reference', 'local_first', 'feature_chunks', 'peer_copy'):
             raise ValueError(f'unknown stage order {self.stage_order!r}')
+        # Stages fused into one product (1 = stage by stage, as the reference).  Peer copies and 1.5D run stage by stage;
+        # the broadcast loop of 1D is fastest with two products per distributed SpMM (half of the stages each): longer
+        # rows per product and one read-modify-write of z instead of P-1, while the second half travels under the first.
+        chosen = stage_group if stage_group is not None else os.environ.get('DIST_GNN_STAGE_GROUP')
+        if chosen is not None:
+            self.stage_group = max(1, int(chosen))
+        elif self.stage_order == 'reference' and rep == 1:
+            self.stage_group = max(1, (len(self.stages()) + 1) // 2)
+        else:
+            self.stage_group = 1
         self.chunk_width = int(os.environ.get('DIST_GNN_CHUNK_WIDTH', 64))
         DistEnv.env = self
 
@@ -141,17 +150,39 @@ class DistEnv:
         they all grow at the same call."""
         comm = self.col_comm
         if comm.peer_capacity() >= floats:
-            return
+            return True
         group = self.world_group if self.rep == 1 else self.col_groups[self.rank_col]
         torch.cuda.synchronize(self.device)
         if comm.peer_capacity() > 0:
             comm.peer_close()
             dist.barrier(group, device_ids=[self.device.index])     # nobody frees a buffer a peer still maps
-        mine = comm.peer_alloc(floats)
+        ok, mine = True, b''
+        try:
+            mine = comm.peer_alloc(floats)
+        except RuntimeError as e:                                   # e.g. CUDA IPC not permitted in this container
+            ok, why = False, str(e)
         handles = [None] * comm.size
-        dist.all_gather_object(handles, mine, group=group)
-        comm.peer_open(handles)
+        dist.all_gather_object(handles, mine if ok else None, group=group)
+        if all(h is not None for h in handles):
+            try:
+                comm.peer_open(handles)
+            except RuntimeError as e:
+                ok, why = False, str(e)
+        else:
+            ok, why = False, locals().get('why', 'a peer could not export its send buffers')
+        verdict = [None] * comm.size
+        dist.all_gather_object(verdict, ok, group=group)
+        if not all(verdict):
+            # every rank takes the same decision: back to the NCCL broadcast loop, which needs no peer mappings
+            if comm.peer_capacity() > 0:
+                comm.peer_close()
+            if self.rank == 0:
+                print(f"[dist-gnn] peer-copy stage order unavailable ({why if not ok else 'on a peer'}); using NCCL broadcasts", flush=True)
+            self.stage_order = 'reference'
+            self.stage_group = max(1, (len(self.stages()) + 1) // 2) if self.rep == 1 else 1
+            return False
         dist.barrier(group, device_ids=[self.device.index])
+        return True
 
     def shutdown(self):
         comms = list({id(c): c for c in (self.row_comm, self.col_comm, self.comm) if c is not None}.values())

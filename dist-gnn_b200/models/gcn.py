@@ -126,8 +126,7 @@ def _stage_loop(env, local_adj_parts, x, z, stages, comm):
         with env.timer.timing_cuda('broadcast+spmm'):
             spmm_cpp.allgather_spmm(comm, plan, x, pack, area, z, widths)
         return z
-    if comm is not None and env.stage_order == 'peer_copy':
-        env.ensure_peer_buffers(n * width)
+    if comm is not None and env.stage_order == 'peer_copy' and env.ensure_peer_buffers(n * width):
         with env.timer.timing_cuda('broadcast+spmm'):
             spmm_cpp.peer_spmm(comm, *ordered_products(env, local_adj_parts, stages, x, rotate=True), x, z, row_comm=env.row_comm)
         return z
