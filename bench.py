@@ -41,7 +41,7 @@ def parse():
     ap.add_argument('--layers', type=int, default=0, help='override the number of GCN layers')
     ap.add_argument('--seed', type=int, default=0)
     ap.add_argument('--stage-group', type=int, default=0, help='stages fused into one product (0 = the default of DistEnv)')
-    ap.add_argument('--stage-order', default=None, choices=['reference', 'local_first', 'feature_chunks', 'peer_copy'],
+    ap.add_argument('--stage-order', default=None, choices=['reference', 'local_first', 'feature_chunks', 'peer_copy', 'peer_compact'],
                     help='order of the products inside a distributed SpMM (default: that of DistEnv)')
     ap.add_argument('--chunk-width', type=int, default=0, help='column chunk width of the feature_chunks order (0 = default 64)')
     ap.add_argument('--dense', default=None, choices=['fp32', '3xtf32', 'tcgen05'],
@@ -294,21 +294,7 @@ def measure_stage_loops(env, g, widths, spmm_cpp):
         x = torch.randn(n, width, device=env.device)
         z = torch.empty_like(x)
         for timed in (False, True):
-            if env.stage_order == 'feature_chunks' and env.rep == 1:
-                plan = group_plans(g.adj_parts, [st.part for st in stages], len(stages))[0]
-                chunks = spmm_cpp.chunk_widths(width, env.chunk_width)
-                spmm_cpp.allgather_spmm(env.col_comm, plan, x, env.recv_buffers(n, max(chunks), tag='pack'),
-                                        env.recv_buffers(n * env.col_comm.size, max(chunks), tag='area'), z, chunks, timed=timed)
-            elif env.stage_order == 'peer_copy' and env.ensure_peer_buffers(n * width):
-                spmm_cpp.peer_spmm(env.col_comm, *ordered_products(env, g.adj_parts, stages, x, rotate=True), x, z,
-                                   row_comm=env.row_comm, timed=timed)
-            elif env.stage_order == 'local_first':
-                spmm_cpp.bcast_spmm_ordered(env.col_comm, *ordered_products(env, g.adj_parts, stages, x), x, z,
-                                            row_comm=env.row_comm, timed=timed, bcast_group=env.stage_group)
-            else:
-                plans = group_plans(g.adj_parts, [st.part for st in stages], group)
-                recv = env.recv_buffers(n * group, width)
-                spmm_cpp.bcast_spmm(env.col_comm, roots, plans, x, recv, z, row_comm=env.row_comm, timed=timed, group=group)
+            gcn_module._stage_loop(env, g.adj_parts, x, z, stages, env.col_comm, timed=timed)     # the model's own dispatcher
             torch.cuda.synchronize()
         t = env.col_comm.last_times()
         vals = torch.tensor([t['comm_ms'], t['spmm_ms'], t['total_ms']], dtype=torch.float64, device=env.device)
@@ -316,6 +302,8 @@ def measure_stage_loops(env, g, widths, spmm_cpp):
         comm_ms, spmm_ms, total_ms = vals.tolist()
         received = sum(1 for st in stages if st.root_in_group != env.col_comm.rank) * n * width * 4
         moved = received if env.stage_order == 'peer_copy' else len(stages) * n * width * 4     # peer copies move remote blocks only
+        if env.stage_order == 'peer_compact' and env.rep == 1:
+            moved = received = sum(gcn_module.compact_exchange(env, g.adj_parts, stages)['stage_rows']) * width * 4
         out[f'F{true_width}'] = {
             'width_on_the_wire': width,
             'bcast_bus_gbs': round(moved / (comm_ms * 1e-3) / 1e9, 2) if comm_ms > 0 else None,

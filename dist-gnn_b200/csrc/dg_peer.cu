@@ -168,19 +168,63 @@ int dg_comm_peer_destroy(dg_comm* c)
     return DG_OK;
 }
 
-extern "C" int dg_peer_spmm(dg_comm* comm, dg_comm* row_comm, int32_t n_stages, const int32_t* roots, float* const* landing,
-                            int32_t n_products, const dg_plan* const* plans, const float* const* vals,
-                            const float* const* operands, const int32_t* last_stage, const float* x_local, int32_t n,
-                            int32_t F, float* z, int timed, void* compute_stream)
+namespace {
+
+// dst[i, :] = x[rows[i], :] for a list of row ids (the rows of this rank's block that one peer's sparse block touches)
+__global__ void k_pack_rows_v4(const float4* __restrict__ x, int64_t ldx4, const int32_t* __restrict__ rows, int64_t n_rows,
+                               int32_t F4, float4* __restrict__ dst)
+{
+    const int64_t total = n_rows * F4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / F4;
+        const int32_t c = (int32_t)(i - r * F4);
+        dst[i] = __ldg(x + (int64_t)__ldg(rows + r) * ldx4 + c);
+    }
+}
+__global__ void k_pack_rows(const float* __restrict__ x, int64_t ldx, const int32_t* __restrict__ rows, int64_t n_rows,
+                            int32_t F, float* __restrict__ dst)
+{
+    const int64_t total = n_rows * F;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / F;
+        dst[i] = __ldg(x + (int64_t)__ldg(rows + r) * ldx + (i - r * F));
+    }
+}
+
+// Packed mode (pack_rows != nullptr): instead of the whole block, the send buffer holds for every reader the rows that
+// reader's sparse block touches, one list after the other (pack_offsets in rows); stage s then pulls stage_rows[s] rows
+// from row offset stage_offsets[s] of its root's send buffer.
+struct PeerPacks {
+    int32_t n_packs = 0;
+    const int32_t* const* rows = nullptr;        // device row-id lists
+    const int64_t* counts = nullptr;             // rows per list
+    const int64_t* offsets = nullptr;            // first row of every list inside this rank's send buffer
+    const int64_t* stage_offsets = nullptr;      // per stage: first row inside the root's send buffer
+    const int64_t* stage_rows = nullptr;         // per stage: rows to pull
+};
+
+int peer_loop(dg_comm* comm, dg_comm* row_comm, const PeerPacks& packs, int32_t n_stages, const int32_t* roots,
+              float* const* landing, int32_t n_products, const dg_plan* const* plans, const float* const* vals,
+              const float* const* operands, const int32_t* last_stage, const float* x_local, int32_t n, int32_t F,
+              float* z, int timed, void* compute_stream)
 {
     cudaStream_t compute = (cudaStream_t)compute_stream;
+    const bool packed = packs.rows != nullptr || packs.stage_rows != nullptr;
     if (!comm) return DG_ERR_NULL;
+    if (packed) {
+        if (packs.n_packs < 0 || (packs.n_packs > 0 && (!packs.rows || !packs.counts || !packs.offsets))) return DG_ERR_NULL;
+        if (n_stages > 0 && (!packs.stage_offsets || !packs.stage_rows)) return DG_ERR_NULL;
+        for (int q = 0; q < packs.n_packs; ++q) {
+            if (packs.counts[q] < 0 || packs.offsets[q] < 0 || (packs.counts[q] > 0 && !packs.rows[q])) return DG_ERR_DIMS;
+            if ((packs.offsets[q] + packs.counts[q]) * (int64_t)F > comm->peer_floats) return DG_ERR_SCRATCH;
+        }
+    }
     if (n_stages < 0 || n_products < 0 || n < 0 || F < 0) return DG_ERR_DIMS;
     if ((n_stages > 0 && (!roots || !landing)) || (n_products > 0 && (!plans || !vals || !operands || !last_stage))) return DG_ERR_NULL;
     const size_t count = (size_t)n * (size_t)F;
     if (count && (!x_local || !z)) return DG_ERR_NULL;
     if (comm->peer_ptr.empty()) return DG_ERR_STATE;              // dg_comm_peer_alloc / _open come first
-    if ((int64_t)count > comm->peer_floats) return DG_ERR_SCRATCH;
+    if (!packed && (int64_t)count > comm->peer_floats) return DG_ERR_SCRATCH;
     for (int s = 0; s < n_stages; ++s) {
         if (roots[s] < 0 || roots[s] >= comm->nranks) return DG_ERR_DIMS;
         if (count && roots[s] != comm->rank && !landing[s]) return DG_ERR_NULL;
@@ -204,7 +248,22 @@ extern "C" int dg_peer_spmm(dg_comm* comm, dg_comm* row_comm, int32_t n_stages, 
     const int b = (int)(comm->peer_loops & 1);
     comm->peer_loops++;
     // this rank's block goes where its peers can read it; everything queued so far on the compute stream comes first
-    if (count) DG_CUDA(cudaMemcpyAsync(comm->peer_send[b], x_local, count * sizeof(float), cudaMemcpyDeviceToDevice, compute));
+    if (packed) {
+        for (int q = 0; q < packs.n_packs && count; ++q) {
+            if (packs.counts[q] == 0) continue;
+            float* dst = comm->peer_send[b] + packs.offsets[q] * (int64_t)F;
+            const int64_t total = packs.counts[q] * (int64_t)(F % 4 == 0 ? F / 4 : F);
+            const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+            if (F % 4 == 0 && (reinterpret_cast<uintptr_t>(x_local) & 15) == 0)
+                k_pack_rows_v4<<<grid, 256, 0, compute>>>(reinterpret_cast<const float4*>(x_local), F / 4, packs.rows[q], packs.counts[q], F / 4,
+                                                          reinterpret_cast<float4*>(dst));
+            else
+                k_pack_rows<<<grid, 256, 0, compute>>>(x_local, F, packs.rows[q], packs.counts[q], F, dst);
+        }
+        DG_CUDA(cudaGetLastError());
+    } else if (count) {
+        DG_CUDA(cudaMemcpyAsync(comm->peer_send[b], x_local, count * sizeof(float), cudaMemcpyDeviceToDevice, compute));
+    }
     DG_CUDA(cudaEventRecord(comm->ev_input, compute));
     DG_CUDA(cudaStreamWaitEvent(comm->side, comm->ev_input, 0));
     DG_NCCL(ncclAllReduce(comm->peer_token, comm->peer_token, 1, ncclFloat, ncclMax, comm->comm, comm->side));
@@ -217,11 +276,17 @@ extern "C" int dg_peer_spmm(dg_comm* comm, dg_comm* row_comm, int32_t n_stages, 
         for (; issued <= last_stage[p]; ++issued) {
             const int s = issued;
             if (!count || roots[s] == comm->rank) {
-                if (count && landing[s])                          // the caller wants its own block inside the landing area too
+                if (count && landing[s] && !packed)               // the caller wants its own block inside the landing area too
                     DG_CUDA(cudaMemcpyAsync(landing[s], x_local, count * sizeof(float), cudaMemcpyDeviceToDevice, comm->side));
                 continue;
             }
-            if ((rc = pull_block(comm, landing[s], comm->peer_ptr[2 * roots[s] + b], count, lanes))) return rc;
+            if (packed) {
+                const size_t part = (size_t)packs.stage_rows[s] * (size_t)F;
+                if (part && (rc = pull_block(comm, landing[s], comm->peer_ptr[2 * roots[s] + b] + packs.stage_offsets[s] * (int64_t)F, part, lanes)))
+                    return rc;
+            } else if ((rc = pull_block(comm, landing[s], comm->peer_ptr[2 * roots[s] + b], count, lanes))) {
+                return rc;
+            }
         }
         if (timed) DG_CUDA(cudaEventRecord(comm->t_comm[2 * p + 1], comm->side));
         if (last_stage[p] >= 0) {
@@ -245,4 +310,32 @@ extern "C" int dg_peer_spmm(dg_comm* comm, dg_comm* row_comm, int32_t n_stages, 
         comm->timed_stages = n_products;
     }
     return DG_OK;
+}
+
+}  // namespace
+
+extern "C" int dg_peer_spmm(dg_comm* comm, dg_comm* row_comm, int32_t n_stages, const int32_t* roots, float* const* landing,
+                            int32_t n_products, const dg_plan* const* plans, const float* const* vals,
+                            const float* const* operands, const int32_t* last_stage, const float* x_local, int32_t n,
+                            int32_t F, float* z, int timed, void* compute_stream)
+{
+    return peer_loop(comm, row_comm, PeerPacks{}, n_stages, roots, landing, n_products, plans, vals, operands, last_stage, x_local, n, F,
+                     z, timed, compute_stream);
+}
+
+extern "C" int dg_peer_spmm_packed(dg_comm* comm, dg_comm* row_comm, int32_t n_packs, const int32_t* const* pack_rows,
+                                   const int64_t* pack_counts, const int64_t* pack_offsets, int32_t n_stages, const int32_t* roots,
+                                   const int64_t* stage_offsets, const int64_t* stage_rows, float* const* landing,
+                                   int32_t n_products, const dg_plan* const* plans, const float* const* vals,
+                                   const float* const* operands, const int32_t* last_stage, const float* x_local, int32_t n,
+                                   int32_t F, float* z, int timed, void* compute_stream)
+{
+    if (!stage_offsets && n_stages > 0) return DG_ERR_NULL;
+    PeerPacks packs;
+    packs.n_packs = n_packs; packs.rows = pack_rows; packs.counts = pack_counts; packs.offsets = pack_offsets;
+    packs.stage_offsets = stage_offsets; packs.stage_rows = stage_rows;
+    static const int64_t none = 0;
+    if (!packs.stage_rows) packs.stage_rows = &none;              // marks packed mode even with no stage to pull
+    return peer_loop(comm, row_comm, packs, n_stages, roots, landing, n_products, plans, vals, operands, last_stage, x_local, n, F, z,
+                     timed, compute_stream);
 }

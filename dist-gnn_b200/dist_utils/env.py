@@ -46,7 +46,8 @@ class DistEnv:
         # of the transfer hidden), reference for 1.5D (peer copies were slower there: 48 against 35 ms).
         default_order = 'peer_copy' if rep == 1 else 'reference'
         self.stage_order = stage_order if stage_order is not None else os.environ.get('DIST_GNN_STAGE_ORDER', default_order)
-        if self.stage_order not in ('reference', 'local_first', 'feature_chunks', 'peer_copy'):
+        # 'peer_compact': peer_copy that moves only the operand rows each reader's sparse block touches (1D)
+        if self.stage_order not in ('reference', 'local_first', 'feature_chunks', 'peer_copy', 'peer_compact'):
             raise ValueError(f'unknown stage order {self.stage_order!r}')
         # Stages fused into one product (1 = stage by stage, as the reference).  Peer copies and 1.5D run stage by stage;
         # the broadcast loop of 1D is fastest with two products per distributed SpMM (half of the stages each): longer

@@ -60,3 +60,15 @@ def pull_order(stage_list, me, size):
     remote = [i for i, st in enumerate(stage_list) if st.root_in_group != me]
     remote.sort(key=lambda i: ((stage_list[i].root_in_group - me) % size, i))
     return own, remote
+
+
+def pack_layout(sizes, owner):
+    """Where every reader's rows start inside `owner`'s send buffer in the 'peer_compact' stage order.  sizes[q][s] is the
+    number of rows of block s that reader q's sparse block touches (0 for q == s: a rank reads its own block in place).
+    Returns (offsets, total): offsets[q] = first row of reader q's list, lists laid out in ascending reader order."""
+    offsets, total = [], 0
+    for q in range(len(sizes)):
+        offsets.append(total)
+        if q != owner:
+            total += int(sizes[q][owner])
+    return offsets, total

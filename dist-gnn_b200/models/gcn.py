@@ -115,7 +115,9 @@ def broadcast(local_adj_parts, local_feature, tag):
     return _stage_loop(env, local_adj_parts, x, z, stages, comm)
 
 
-def _stage_loop(env, local_adj_parts, x, z, stages, comm):
+def _stage_loop(env, local_adj_parts, x, z, stages, comm, timed=False):
+    """z <- sum over the stages of A[rank, s] @ X_s by the schedule env.stage_order names (timed: leave per-product event
+    pairs behind for Comm.last_times)."""
     n, width = x.shape
     if comm is not None and env.stage_order == 'feature_chunks' and env.rep == 1:
         # 1D only: pipeline along the feature dimension (all-gather of column chunks, full-length rows per product)
@@ -124,23 +126,84 @@ def _stage_loop(env, local_adj_parts, x, z, stages, comm):
         pack = env.recv_buffers(n, max(widths), nbuf=2, tag='pack')
         area = env.recv_buffers(n * comm.size, max(widths), nbuf=2, tag='area')
         with env.timer.timing_cuda('broadcast+spmm'):
-            spmm_cpp.allgather_spmm(comm, plan, x, pack, area, z, widths)
+            spmm_cpp.allgather_spmm(comm, plan, x, pack, area, z, widths, timed=timed)
         return z
-    if comm is not None and env.stage_order == 'peer_copy' and env.ensure_peer_buffers(n * width):
+    if comm is not None and env.stage_order == 'peer_compact' and env.rep == 1:
+        ex = compact_exchange(env, local_adj_parts, stages)
+        if env.ensure_peer_buffers(ex['send_rows'] * width):
+            area = env.recv_buffers(max(ex['area_rows'], 1), width, nbuf=1, tag='compact')[0]
+            landing = [None] * len(ex['own']) + [area[o:o + r] for o, r in zip(ex['area_offsets'], ex['stage_rows'])]
+            products = [(spmm_cpp.plan_for(local_adj_parts[stages[i].part]), x, -1) for i in ex['own']]
+            products += [(plan, block, len(ex['own']) + j) for j, (plan, block) in enumerate(zip(ex['plans'], landing[len(ex['own']):]))]
+            zeros = [0] * len(ex['own'])
+            with env.timer.timing_cuda('broadcast+spmm'):
+                spmm_cpp.peer_spmm_packed(comm, ex['packs'], ex['roots'], zeros + ex['stage_offsets'], zeros + ex['stage_rows'], landing,
+                                          products, x, z, timed=timed)
+            return z
+    if comm is not None and env.stage_order in ('peer_copy', 'peer_compact') and env.ensure_peer_buffers(n * width):
         with env.timer.timing_cuda('broadcast+spmm'):
-            spmm_cpp.peer_spmm(comm, *ordered_products(env, local_adj_parts, stages, x, rotate=True), x, z, row_comm=env.row_comm)
+            spmm_cpp.peer_spmm(comm, *ordered_products(env, local_adj_parts, stages, x, rotate=True), x, z, row_comm=env.row_comm,
+                               timed=timed)
         return z
     if comm is not None and env.stage_order == 'local_first':
         with env.timer.timing_cuda('broadcast+spmm'):
             spmm_cpp.bcast_spmm_ordered(comm, *ordered_products(env, local_adj_parts, stages, x), x, z,
-                                        row_comm=env.row_comm, bcast_group=env.stage_group)
+                                        row_comm=env.row_comm, bcast_group=env.stage_group, timed=timed)
         return z
     group = min(env.stage_group, len(stages)) if comm is not None else 1
     plans = group_plans(local_adj_parts, [st.part for st in stages], group)
     recv = env.recv_buffers(n * group, width) if comm is not None else None
     with env.timer.timing_cuda('broadcast+spmm'):
-        spmm_cpp.bcast_spmm(comm, [st.root_in_group for st in stages], plans, x, recv, z, row_comm=env.row_comm, group=group)
+        spmm_cpp.bcast_spmm(comm, [st.root_in_group for st in stages], plans, x, recv, z, row_comm=env.row_comm, group=group,
+                            timed=timed)
     return z
+
+
+_compact_cache = {}
+
+
+def compact_exchange(env, adj_parts, stages):
+    """One-off set-up of the 'peer_compact' stage order for this rank's blocks (1D).  For every remote block: the sorted
+    list of the columns it touches, a plan whose column ids are positions in that list, and - after one exchange of the
+    lists - where this rank's rows start inside each owner's send buffer and which rows this rank packs for every
+    reader.  Collective over the column communicator's ranks (an all-gather of the lists as host objects)."""
+    import torch.distributed as dist
+    hit = _compact_cache.get(id(adj_parts))
+    if hit is not None and hit[0] is adj_parts:
+        return hit[1]
+    comm = env.col_comm
+    me, size = comm.rank, comm.size
+    own, remote = schedule.pull_order(stages, me, size)
+    n = adj_parts[0].size(0)
+    wanted, plans, kept = {}, [], []
+    for i in remote:
+        block = adj_parts[stages[i].part]
+        idx = block.indices()
+        if idx.size(1) == 0:
+            continue                                                  # an empty block adds nothing: no list, no copy, no product
+        touched = torch.unique(idx[1])                                # ascending
+        position = torch.searchsorted(touched, idx[1].contiguous())
+        plans.append(spmm_cpp.SpmmPlan(idx[0].to(torch.int32), position.to(torch.int32).contiguous(), block.values().contiguous(),
+                                       n, touched.numel()))
+        wanted[stages[i].root_in_group] = touched.to(torch.int32).cpu().numpy()
+        kept.append(i)
+    gathered = [None] * size
+    dist.all_gather_object(gathered, wanted, group=env.world_group)   # gathered[q][s]: rows of block s that reader q needs
+    sizes = [[len(gathered[q].get(s, ())) for s in range(size)] for q in range(size)]
+    layouts = [schedule.pack_layout(sizes, s) for s in range(size)]
+    my_offsets = layouts[me][0]
+    packs = [(torch.from_numpy(gathered[q][me]).to(env.device), my_offsets[q]) for q in range(size) if q != me and sizes[q][me] > 0]
+    roots = [stages[i].root_in_group for i in own + kept]
+    stage_rows = [sizes[me][stages[i].root_in_group] for i in kept]
+    area_offsets, total = [], 0
+    for r in stage_rows:
+        area_offsets.append(total)
+        total += r
+    ex = dict(own=own, remote=kept, plans=plans, packs=packs, roots=roots, stage_rows=stage_rows,
+              stage_offsets=[layouts[stages[i].root_in_group][0][me] for i in kept], area_offsets=area_offsets, area_rows=total,
+              send_rows=max(max(t for _, t in layouts), 1), sizes=sizes)
+    _compact_cache[id(adj_parts)] = (adj_parts, ex)
+    return ex
 
 
 def ordered_products(env, adj_parts, stages, x, rotate=False):

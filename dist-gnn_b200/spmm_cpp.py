@@ -77,6 +77,7 @@ def lib():
             'dg_comm_peer_open': ([vp, ctypes.c_char_p], ctypes.c_int),
             'dg_comm_peer_close': ([vp], ctypes.c_int),
             'dg_comm_peer_capacity': ([vp], ctypes.c_int64),
+            'dg_peer_spmm_packed': ([vp, vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, vp, ctypes.c_int, vp], ctypes.c_int),
             'dg_peer_spmm': ([vp, vp, i32, vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, vp, ctypes.c_int, vp], ctypes.c_int),
             'dg_dense_split': ([vp, vp, vp, i64, vp], ctypes.c_int),
             'dg_dense_supported': ([i64, i32, i32, i64, i64, vp, vp, vp], ctypes.c_int),
@@ -394,6 +395,40 @@ def peer_spmm(comm, roots, landing, products, x_local, z, row_comm=None, timed=F
     """dg_peer_spmm: the arguments of bcast_spmm_ordered, but every remote block is pulled from its root's send buffer
     by a device-to-device copy (Comm.peer_alloc / peer_open come first) and the stage order may differ per rank."""
     return bcast_spmm_ordered(comm, roots, landing, products, x_local, z, row_comm=row_comm, timed=timed, peer_copies=True)
+
+
+def peer_spmm_packed(comm, packs, roots, stage_offsets, stage_rows, landing, products, x_local, z, row_comm=None, timed=False):
+    """dg_peer_spmm_packed: peer_spmm that moves only the operand rows each reader's sparse block touches.
+
+    packs          list of (row-id tensor (int32, CUDA, ascending), first row inside this rank's send buffer), one per reader
+    roots[s], stage_offsets[s], stage_rows[s]   root of stage s, first row of this rank's list inside the root's send
+                   buffer, and its length;  landing[s]: (stage_rows[s] x F) tensor, or None at an own stage
+    products       (plan, operand, last_stage) as for peer_spmm; the plans of remote blocks use the packed numbering"""
+    _dev_tensor(x_local, torch.float32, 'x_local'), _dev_tensor(z, torch.float32, 'z')
+    n, F = x_local.shape
+    Q, S, P = len(packs), len(roots), len(products)
+    for rows, _ in packs:
+        _dev_tensor(rows, torch.int32, 'pack row ids')
+    pr = (ctypes.c_void_p * max(Q, 1))(*[rows.data_ptr() if rows.numel() else None for rows, _ in packs])
+    pc = (ctypes.c_int64 * max(Q, 1))(*[rows.numel() for rows, _ in packs])
+    po = (ctypes.c_int64 * max(Q, 1))(*[int(off) for _, off in packs])
+    roots_arr = (ctypes.c_int32 * max(S, 1))(*roots)
+    so = (ctypes.c_int64 * max(S, 1))(*[int(v) for v in stage_offsets])
+    sr = (ctypes.c_int64 * max(S, 1))(*[int(v) for v in stage_rows])
+    land_arr = (ctypes.c_void_p * max(S, 1))(*[None if t is None or t.numel() == 0 else _dev_tensor(t, torch.float32, 'landing block').data_ptr()
+                                                for t in landing])
+    for plan, operand, _ in products:
+        _dev_tensor(operand, torch.float32, 'operand')
+        if operand.size(0) != plan.k or operand.size(1) != F:
+            raise RuntimeError(f'operand {tuple(operand.shape)} does not match a plan with {plan.k} columns and width {F}')
+    plan_arr = (ctypes.c_void_p * max(P, 1))(*[p.handle for p, _, _ in products])
+    val_arr = (ctypes.c_void_p * max(P, 1))(*[p.values.data_ptr() for p, _, _ in products])
+    op_arr = (ctypes.c_void_p * max(P, 1))(*[t.data_ptr() for _, t, _ in products])
+    last_arr = (ctypes.c_int32 * max(P, 1))(*[l for _, _, l in products])
+    with torch.cuda.device(x_local.device):
+        check(lib().dg_peer_spmm_packed(comm.handle, row_comm.handle if row_comm else None, Q, pr, pc, po, S, roots_arr, so, sr, land_arr,
+                                        P, plan_arr, val_arr, op_arr, last_arr, x_local.data_ptr(), n, F, z.data_ptr(), int(timed), _stream()))
+    return z
 
 
 def chunk_widths(F, target=64):

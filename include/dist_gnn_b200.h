@@ -195,6 +195,19 @@ int dg_peer_spmm(dg_comm* comm, dg_comm* row_comm, int32_t n_stages, const int32
                  int32_t n_products, const dg_plan* const* host_plans, const float* const* host_vals,
                  const float* const* host_operands, const int32_t* host_last_stage, const float* x_local, int32_t n,
                  int32_t F, float* z, int timed, void* compute_stream);
+/* dg_peer_spmm moving only the rows that are needed.  A sparse block A[r, s] touches a subset of the rows of X_s (on
+ * skewed graphs less than half at 8 ranks); the owner s packs, for every reader r, exactly those rows into its send
+ * buffer (host_pack_rows[q]: device list of row ids of x_local, ascending; list q starts at row host_pack_offsets[q] of
+ * the send buffer) and reader r pulls host_stage_rows[s] rows starting at row host_stage_offsets[s] of the root's send
+ * buffer.  The reader's plan for that block must use the packed numbering (column id = position in its list), so the
+ * arithmetic per output row, and its order, are those of the unpacked product.  The lists are fixed per graph: the
+ * readers compute them once and hand them to the owners.  Own stages (host_roots[s] == rank) are read from x_local. */
+int dg_peer_spmm_packed(dg_comm* comm, dg_comm* row_comm, int32_t n_packs, const int32_t* const* host_pack_rows,
+                        const int64_t* host_pack_counts, const int64_t* host_pack_offsets, int32_t n_stages,
+                        const int32_t* host_roots, const int64_t* host_stage_offsets, const int64_t* host_stage_rows,
+                        float* const* host_landing, int32_t n_products, const dg_plan* const* host_plans,
+                        const float* const* host_vals, const float* const* host_operands, const int32_t* host_last_stage,
+                        const float* x_local, int32_t n, int32_t F, float* z, int timed, void* compute_stream);
 /* 1D only: the same distributed product pipelined along the feature dimension (replaces gcn.py:16-30 as a whole).  The
  * n x F operand is cut into n_chunks column chunks (host_chunk_widths, summing to F).  Chunk c of every rank is
  * all-gathered on the side stream into host_area[c % 2] ((nranks*n) x w_c, rank r's rows at r*n) while the compute

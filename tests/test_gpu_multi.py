@@ -64,6 +64,8 @@ def _worker(rank, world, rep, port, out_dir, mode):
                 rec[f'zp{i}'] = broadcast(g.adj_parts, x, f'w{width}').cpu().numpy()
                 env.stage_group = 2
                 rec[f'zpg{i}'] = broadcast(g.adj_parts, x, f'w{width}').cpu().numpy()
+                env.stage_group, env.stage_order = 1, 'peer_compact'    # only the rows each reader's block touches travel (1D)
+                rec[f'zc{i}'] = broadcast(g.adj_parts, x, f'w{width}').cpu().numpy()
                 env.stage_group, env.stage_order = 1, 'reference'
         torch.cuda.synchronize()
         np.savez(os.path.join(out_dir, f'rank{rank}.npz'), **rec)
@@ -108,7 +110,7 @@ def test_back_to_back_stage_loops_at_two_ranks(golden):
         want = ref_gcn.broadcast_1d([p['adj_parts'] for p in parts], [res[r][f'x{i}'] for r in range(2)])
         for r in range(2):
             assert_close(res[r][f'z{i}'], want[r], 1e-5, f'loop {i} rank {r}')
-            for key in ('zg', 'zl', 'zlg', 'zf', 'zp', 'zpg'):
+            for key in ('zg', 'zl', 'zlg', 'zf', 'zp', 'zpg', 'zc'):
                 assert_close(res[r][f'{key}{i}'], want[r], 1e-5, f'{key} loop {i} rank {r}')
 
 
@@ -121,5 +123,5 @@ def test_15d_stage_loop_at_four_ranks(golden):
         want = ref_gcn.broadcast_15d([p['adj_parts'] for p in parts], [res[b * 2][f'x{i}'] for b in range(2)], 4, 2)
         for r in range(4):
             assert_close(res[r][f'z{i}'], want[r], 1e-5, f'loop {i} rank {r}')
-            for key in ('zg', 'zl', 'zlg', 'zf', 'zp', 'zpg'):
+            for key in ('zg', 'zl', 'zlg', 'zf', 'zp', 'zpg', 'zc'):
                 assert_close(res[r][f'{key}{i}'], want[r], 1e-5, f'{key} loop {i} rank {r}')

@@ -162,3 +162,13 @@ def test_pull_order_of_the_peer_copy_loop():
             own, remote = schedule.pull_order(st, me, P // c)
             assert sorted(own + remote) == list(range(len(st)))
             assert all(st[i].root_in_group == me for i in own) and all(st[i].root_in_group != me for i in remote)
+
+
+def test_pack_layout_of_the_compact_peer_loop():
+    """Readers' row lists lie one after the other in the owner's send buffer, in reader order, the owner itself taking
+    no room; every rank derives the same layout from the gathered sizes."""
+    from dist_utils import schedule
+    sizes = [[0, 5, 2], [7, 0, 0], [3, 4, 0]]          # sizes[q][s]: rows of block s that reader q needs
+    assert schedule.pack_layout(sizes, 0) == ([0, 0, 7], 10)
+    assert schedule.pack_layout(sizes, 1) == ([0, 5, 5], 9)
+    assert schedule.pack_layout(sizes, 2) == ([0, 2, 2], 2)
