@@ -35,6 +35,8 @@ struct DenseArgs {
     uint32_t relu;
     const float* mask;              // optional [M x N]: the result is zeroed where mask <= 0 (ReLU backward), else nullptr
     int64_t ldm;
+    int32_t raw_head;               // persistent kernel: 0 = masked head copy; 1 = the fp32 tile itself serves as head;
+                                    // 2 = as 1, and the two head passes of a slab are issued before its tail is ready
     int* status;
 };
 
@@ -342,12 +344,32 @@ k_dense_nt_persistent(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 const uint32_t acc = tmem + (uint32_t)(b * 256);
                 for (int i = 0; i < nslabs; ++i, ++it) {
                     const int s = it % STAGES, u = it / STAGES;
-                    ok = mbar_wait(ready0 + 8 * s, u & 1);
-                    if (!ok) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t st = base + s * stage_bytes;
                     const uint64_t a_head = umma_desc_sw128(st), a_tail = umma_desc_sw128(st + BM * 128);
                     const uint64_t b_head = umma_desc_sw128(st + 2 * BM * 128), b_tail = umma_desc_sw128(st + 2 * BM * 128 + b_bytes);
+                    if (a.raw_head == 2) {
+                        // The tensor cores read a TF32 operand from a 32-bit container and ignore its low 13 bits, so the
+                        // tile as TMA delivered it IS the head: both head passes go out as soon as the data has landed,
+                        // and only the tail pass waits for the split warps.
+                        ok = mbar_wait(full0 + 8 * s, u & 1);
+                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                        for (int k = 0; k < BK / 8; ++k) {
+                            umma_tf32(acc, a_head + 2 * k, b_tail + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                            umma_tf32(acc, a_head + 2 * k, b_head + 2 * k, idesc, 1u);
+                        }
+                        ok = mbar_wait(ready0 + 8 * s, u & 1);
+                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                        for (int k = 0; k < BK / 8; ++k) umma_tf32(acc, a_tail + 2 * k, b_head + 2 * k, idesc, 1u);
+                        umma_commit(empty0 + 8 * s);
+                        continue;
+                    }
+                    ok = mbar_wait(ready0 + 8 * s, u & 1);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                     for (int k = 0; k < BK / 8; ++k) {
                         umma_tf32(acc, a_tail + 2 * k, b_head + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
@@ -375,7 +397,7 @@ k_dense_nt_persistent(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                     float4 h;
                     h.x = __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u); h.y = __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
                     h.z = __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u); h.w = __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
-                    head[j] = h;
+                    if (!a.raw_head) head[j] = h;
                     tail[j] = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -535,6 +557,10 @@ extern "C" int dg_dense_nt_masked(const float* A, int64_t lda, const float* Bt_h
     DenseArgs a{};
     a.C = C; a.ldc = ldc; a.M = M; a.N = N; a.K = K; a.n_pad = (N + 15) / 16 * 16; a.relu = relu ? 1u : 0u;
     a.mask = mask; a.ldm = ldm;
+    // Measured: the tensor cores ignore the low 13 bits of a TF32 operand (results with and without the masked head copy are
+    // bit-identical), so the tile as loaded serves as head; issuing the head passes before the split is 4 % faster.
+    static const int raw_env = [] { const char* v = getenv("DG_DENSE_RAW_HEAD"); return v ? atoi(v) : 2; }();
+    a.raw_head = raw_env;
     a.status = dense_status_word();
     if (!a.status) return DG_ERR_STATE;
     CUtensorMap tmA, tmBh, tmBt;
@@ -592,6 +618,7 @@ struct DenseTnArgs {
     int64_t rows_per_cta;                       // multiple of TN_ROWS
     int32_t Km, Nn, n_pad, m_halves;            // n_pad: Nn rounded up to 16; m_halves: 1 (Km <= 128) or 2
     int32_t flush_slabs;                        // slabs accumulated in tensor memory between two flushes
+    int32_t raw_head;                           // as DenseArgs::raw_head
     int* status;
 };
 
@@ -684,11 +711,42 @@ k_dense_tn(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUte
                 const int s = i % TN_STAGES, u = i / TN_STAGES;
                 const int grp = i / T, in_grp = i % T;            // the accumulators restart with every flush group
                 if (in_grp == 0 && grp > 0) ok = mbar_wait(acc_empty, (grp - 1) & 1);
-                if (ok) ok = mbar_wait(ready0 + 8 * s, u & 1);
                 if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t st = base + s * stage_bytes;
                 const uint64_t g_head = umma_desc_mn_sw128(st + 2 * x_bytes), g_tail = umma_desc_mn_sw128(st + 2 * x_bytes + g_bytes);
+                if (a.raw_head == 2) {
+                    // the tiles as TMA delivered them serve as heads (the low 13 bits of a TF32 operand are ignored): the
+                    // head x head pass does not wait for the split
+                    ok = mbar_wait(full0 + 8 * s, u & 1);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    for (int h = 0; h < a.m_halves; ++h) {
+                        const uint64_t x_head = umma_desc_mn_sw128(st + h * 4 * TN_BOX_BYTES);
+#pragma unroll
+                        for (int k = 0; k < TN_ROWS / 8; ++k)
+                            umma_tf32(tmem + (uint32_t)(h * 256), x_head + (uint64_t)(k * (1024 >> 4)), g_head + (uint64_t)(k * (1024 >> 4)), idesc,
+                                      (in_grp > 0 || k > 0) ? 1u : 0u);
+                    }
+                    ok = mbar_wait(ready0 + 8 * s, u & 1);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    for (int h = 0; h < a.m_halves; ++h) {
+                        const uint64_t x_head = umma_desc_mn_sw128(st + h * 4 * TN_BOX_BYTES);
+                        const uint64_t x_tail = umma_desc_mn_sw128(st + x_bytes + h * 4 * TN_BOX_BYTES);
+#pragma unroll
+                        for (int k = 0; k < TN_ROWS / 8; ++k) {
+                            const uint64_t adv = (uint64_t)(k * (1024 >> 4));
+                            umma_tf32(tmem + (uint32_t)(h * 256), x_tail + adv, g_head + adv, idesc, 1u);
+                            umma_tf32(tmem + (uint32_t)(h * 256), x_head + adv, g_tail + adv, idesc, 1u);
+                        }
+                    }
+                    umma_commit(empty0 + 8 * s);
+                    if (in_grp == T - 1 || i == nslabs - 1) umma_commit(acc_full);
+                    continue;
+                }
+                ok = mbar_wait(ready0 + 8 * s, u & 1);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 for (int h = 0; h < a.m_halves; ++h) {
                     const uint64_t x_head = umma_desc_mn_sw128(st + h * 4 * TN_BOX_BYTES);
                     const uint64_t x_tail = umma_desc_mn_sw128(st + x_bytes + h * 4 * TN_BOX_BYTES);
@@ -723,7 +781,7 @@ k_dense_tn(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUte
                     float4 h;
                     h.x = __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u); h.y = __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
                     h.z = __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u); h.w = __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
-                    head[j] = h;
+                    if (!a.raw_head) head[j] = h;
                     tail[j] = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
                 }
             }
@@ -828,6 +886,9 @@ extern "C" int dg_dense_tn(const float* X, int64_t ldx, const float* G, int64_t 
     const int64_t slots = (int64_t)a.m_halves * 128 * a.n_pad;    // one CTA's partial, padding included
     if (ctas * slots > scratch_floats) return DG_ERR_SCRATCH;
     static const int flush_env = [] { const char* v = getenv("DG_DENSE_TN_FLUSH"); return v ? atoi(v) : 0; }();
+    // 1: no masked head copies (bit-identical results, fewer shared-memory writes); 2 (head x head before the split) is not faster here
+    static const int raw_env = [] { const char* v = getenv("DG_DENSE_RAW_HEAD"); return v ? atoi(v) : 1; }();
+    a.raw_head = raw_env;
     a.flush_slabs = flush_env > 0 ? flush_env : 16;               // 256 rows = 96 tensor-core accumulations per chain
     a.partial = scratch;
     a.status = dense_status_word();

@@ -171,9 +171,9 @@ class DistEnv:
                 ok, why = False, str(e)
         else:
             ok, why = False, locals().get('why', 'a peer could not export its send buffers')
-        verdict = [None] * comm.size
-        dist.all_gather_object(verdict, ok, group=group)
-        if not all(verdict):
+        agreed = [None] * comm.size
+        dist.all_gather_object(agreed, ok, group=group)
+        if not all(agreed):
             # every rank takes the same decision: back to the NCCL broadcast loop, which needs no peer mappings
             if comm.peer_capacity() > 0:
                 comm.peer_close()
