@@ -42,11 +42,12 @@ class DistEnv:
         # 'local_first': own block first, one receive area for all remote blocks, every broadcast queued up front;
         # 'feature_chunks' (1D): all-gather the operand one column chunk at a time, one full-row product per chunk;
         # 'peer_copy':   own block first, remote blocks pulled from their owners' send buffers by device-to-device copies.
-        # Default: peer_copy for 1D (fastest at 2 and 8 GPUs: 39.9 / 25.4 ms against 48.2 / 27.4 for 'reference', with 0.8-0.9
-        # of the transfer hidden), reference for 1.5D (peer copies were slower there: 48 against 35 ms).
-        default_order = 'peer_copy' if rep == 1 else 'reference'
+        # 'peer_compact': peer_copy that moves only the operand rows each reader's sparse block touches (1D; less than half
+        #                of the rows at 8 ranks on the benchmark graph).
+        # Default: peer_compact for 1D (2 GPUs: 37.8 ms against 38.6 for peer_copy and 48.2 for 'reference'; peer_copy at 8
+        # GPUs: 25.4 against 27.4, with 0.8-0.9 of the transfer hidden), reference for 1.5D (peer copies were slower there).
+        default_order = 'peer_compact' if rep == 1 else 'reference'
         self.stage_order = stage_order if stage_order is not None else os.environ.get('DIST_GNN_STAGE_ORDER', default_order)
-        # 'peer_compact': peer_copy that moves only the operand rows each reader's sparse block touches (1D)
         if self.stage_order not in ('reference', 'local_first', 'feature_chunks', 'peer_copy', 'peer_compact'):
             raise ValueError(f'unknown stage order {self.stage_order!r}')
         # Stages fused into one product (1 = stage by stage, as the reference).  Peer copies and 1.5D run stage by stage;

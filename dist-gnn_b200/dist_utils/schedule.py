@@ -72,3 +72,24 @@ def pack_layout(sizes, owner):
         if q != owner:
             total += int(sizes[q][owner])
     return offsets, total
+
+
+def compact_layout(gathered, me, remote_roots):
+    """Bookkeeping of the 'peer_compact' stage order for rank `me`, from the lists every rank asked for.
+    gathered[q][s]   the ascending row ids of block s that reader q needs (absent or empty: nothing)
+    remote_roots     the roots of this rank's remote stages, in the order it pulls them
+    Returns a dict:  sizes (sizes[q][s]), packs [(reader q, first row of q's list inside this rank's send buffer)],
+    stage_offsets / stage_rows per remote stage (where this rank's list starts inside the root's send buffer, its
+    length), area_offsets / area_rows (where the pulled lists land on this rank, side by side in pull order) and
+    send_rows (rows of the largest send buffer over all ranks: every rank allocates that much)."""
+    size = len(gathered)
+    sizes = [[len(gathered[q].get(s, ())) if q != s else 0 for s in range(size)] for q in range(size)]
+    layouts = [pack_layout(sizes, s) for s in range(size)]
+    packs = [(q, layouts[me][0][q]) for q in range(size) if q != me and sizes[q][me] > 0]
+    stage_rows = [sizes[me][r] for r in remote_roots]
+    area_offsets, total = [], 0
+    for rows in stage_rows:
+        area_offsets.append(total)
+        total += rows
+    return dict(sizes=sizes, packs=packs, stage_offsets=[layouts[r][0][me] for r in remote_roots], stage_rows=stage_rows,
+                area_offsets=area_offsets, area_rows=total, send_rows=max(max(t for _, t in layouts), 1))

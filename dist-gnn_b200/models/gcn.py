@@ -189,19 +189,11 @@ def compact_exchange(env, adj_parts, stages):
         kept.append(i)
     gathered = [None] * size
     dist.all_gather_object(gathered, wanted, group=env.world_group)   # gathered[q][s]: rows of block s that reader q needs
-    sizes = [[len(gathered[q].get(s, ())) for s in range(size)] for q in range(size)]
-    layouts = [schedule.pack_layout(sizes, s) for s in range(size)]
-    my_offsets = layouts[me][0]
-    packs = [(torch.from_numpy(gathered[q][me]).to(env.device), my_offsets[q]) for q in range(size) if q != me and sizes[q][me] > 0]
-    roots = [stages[i].root_in_group for i in own + kept]
-    stage_rows = [sizes[me][stages[i].root_in_group] for i in kept]
-    area_offsets, total = [], 0
-    for r in stage_rows:
-        area_offsets.append(total)
-        total += r
-    ex = dict(own=own, remote=kept, plans=plans, packs=packs, roots=roots, stage_rows=stage_rows,
-              stage_offsets=[layouts[stages[i].root_in_group][0][me] for i in kept], area_offsets=area_offsets, area_rows=total,
-              send_rows=max(max(t for _, t in layouts), 1), sizes=sizes)
+    lay = schedule.compact_layout(gathered, me, [stages[i].root_in_group for i in kept])
+    packs = [(torch.from_numpy(gathered[q][me]).to(env.device), offset) for q, offset in lay['packs']]
+    ex = dict(own=own, remote=kept, plans=plans, packs=packs, roots=[stages[i].root_in_group for i in own + kept],
+              stage_rows=lay['stage_rows'], stage_offsets=lay['stage_offsets'], area_offsets=lay['area_offsets'],
+              area_rows=lay['area_rows'], send_rows=lay['send_rows'], sizes=lay['sizes'])
     _compact_cache[id(adj_parts)] = (adj_parts, ex)
     return ex
 

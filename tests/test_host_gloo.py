@@ -172,3 +172,52 @@ def test_pack_layout_of_the_compact_peer_loop():
     assert schedule.pack_layout(sizes, 0) == ([0, 0, 7], 10)
     assert schedule.pack_layout(sizes, 1) == ([0, 5, 5], 9)
     assert schedule.pack_layout(sizes, 2) == ([0, 2, 2], 2)
+
+
+@pytest.mark.parametrize('P', [2, 3, 4, 8])
+def test_compact_peer_loop_bookkeeping_simulated_on_the_host(P):
+    """The index bookkeeping of the 'peer_compact' stage order (lists of touched rows, pack layout inside the owners' send
+    buffers, pull offsets, re-numbered blocks), run for all P ranks at once in NumPy: every rank's result equals the plain
+    sum over the stages A[r, s] @ X_s, and no reader ever pulls a row it did not ask for."""
+    from dist_utils import schedule
+    rng = np.random.default_rng(P)
+    n, F = 37, 5
+    A = [[(rng.random((n, n)) < 0.06) * rng.standard_normal((n, n)) for _ in range(P)] for _ in range(P)]   # A[r][s]
+    A[1][0][:] = 0.0                                                                      # an empty block
+    X = [rng.standard_normal((n, F)) for _ in range(P)]
+    per_rank = []
+    for me in range(P):
+        stages = schedule.stages(me, P, 1)
+        own, remote = schedule.pull_order(stages, me, P)
+        wanted, kept, blocks = {}, [], []
+        for i in remote:
+            root = stages[i].root_in_group
+            touched = np.flatnonzero(np.abs(A[me][stages[i].part]).sum(axis=0))
+            if touched.size == 0:
+                continue
+            wanted[root] = touched.astype(np.int32)
+            kept.append(i)
+            blocks.append(A[me][stages[i].part][:, touched])                              # columns re-numbered to list positions
+        per_rank.append(dict(stages=stages, own=own, kept=kept, wanted=wanted, blocks=blocks))
+    gathered = [r['wanted'] for r in per_rank]
+    lays = [schedule.compact_layout(gathered, me, [per_rank[me]['stages'][i].root_in_group for i in per_rank[me]['kept']]) for me in range(P)]
+    assert len({lay['send_rows'] for lay in lays}) == 1                                   # every rank allocates the same size
+    send = []
+    for s in range(P):                                                                    # owners pack
+        buf = np.full((lays[s]['send_rows'], F), np.nan)
+        for q, offset in lays[s]['packs']:
+            rows = gathered[q][s]
+            buf[offset:offset + len(rows)] = X[s][rows]
+        send.append(buf)
+    for me in range(P):                                                                   # readers pull and multiply
+        r, lay = per_rank[me], lays[me]
+        z = sum(A[me][r['stages'][i].part] @ X[me] for i in r['own'])
+        area = np.full((max(lay['area_rows'], 1), F), np.nan)
+        for j, i in enumerate(r['kept']):
+            root = r['stages'][i].root_in_group
+            pulled = send[root][lay['stage_offsets'][j]:lay['stage_offsets'][j] + lay['stage_rows'][j]]
+            assert np.array_equal(pulled, X[root][gathered[me][root]])
+            area[lay['area_offsets'][j]:lay['area_offsets'][j] + lay['stage_rows'][j]] = pulled
+            z = z + r['blocks'][j] @ area[lay['area_offsets'][j]:lay['area_offsets'][j] + lay['stage_rows'][j]]
+        want = sum(A[me][s] @ X[s] for s in range(P))
+        assert np.allclose(z, want, rtol=1e-12, atol=1e-12)
