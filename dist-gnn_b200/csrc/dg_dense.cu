@@ -6,13 +6,17 @@
 // bits) and its residual tail, and the accumulator (fp32, in tensor memory) receives
 //     A_head*B_head + A_head*B_tail + A_tail*B_head
 // (the dropped tail*tail term is 2^-22 relative).  The small matrix Bt is split once on the host side of the call
-// (dg_dense_split); A is split inside the kernel, in shared memory, on its way from TMA to the MMA.
+// (dg_dense_split); A is split inside the kernel, in shared memory, on its way from TMA to the MMA.  The tensor cores
+// ignore the low 13 bits of a TF32 operand (verified: identical bits with and without a masked copy), so the tile as
+// loaded serves as head and only the tail is written.
 //
-// One CTA computes a 128-row tile.  Warp 0 drives TMA (128B-swizzled boxes of 32 K-columns: A rows, Bt head, Bt tail)
-// through a 2-stage ring; warps 2-5 split A in place (head) and into a second buffer (tail), fence it to the async
-// proxy and later drain the accumulator (tcgen05.ld) to global memory with the optional ReLU; one thread of warp 1 issues
-// the tcgen05.mma instructions (kind::tf32, 128 x N x 8, operands described by shared-memory matrix descriptors,
-// accumulator in 256 TMEM columns) and commits them to the mbarriers that recycle the stages.
+// k_dense_nt: one CTA per 128-row tile.  Warp 0 drives TMA (128B-swizzled boxes of 32 K-columns: A rows, Bt head, Bt tail)
+// through a 2-stage ring; warps 2-5 split A and later drain the accumulator (tcgen05.ld) to global memory with the
+// optional ReLU / ReLU-backward mask; one thread of warp 1 issues the tcgen05.mma instructions (kind::tf32, 128 x N x 8,
+// operands described by shared-memory matrix descriptors, accumulator in TMEM columns) and commits them to the mbarriers
+// that recycle the stages.  k_dense_nt_persistent: one CTA per SM walks the tiles with two accumulators and separate
+// epilogue warps (used for results wider than 128 columns).  k_dense_tn (further down): the weight gradient X^T * G,
+// both operands MN-major, split-K over the CTAs with periodic accumulator flushes.
 // Every mbarrier wait is bounded; a role that gives up sets the status word and the CTA still frees its TMEM.
 #include <cuda.h>
 #include <cstdint>
