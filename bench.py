@@ -27,7 +27,7 @@ import torch  # noqa: E402
 
 METRIC, UNIT = 'gcn_epoch_ms', 'ms'
 CPU_SAMPLE_PARTS = 16     # the CPU legs time one rank's share of a 16-way 1D row partition and scale by 16
-DRAM_BYTES_PER_ENTRY_FLOAT = 1.375   # measured DRAM traffic of a product per (stored entry x float of width), see roofline
+DRAM_BYTES_PER_ENTRY_FLOAT = 1.57    # measured DRAM traffic of a product per (stored entry x float of width), see roofline
 
 
 def parse():
@@ -253,8 +253,8 @@ def run_ours(args):
                    'stage_order': env.stage_order, 'stage_group': env.stage_group, 'dense': gcn_module.DENSE_MODE},
         'roofline': {'bound': 'hbm', 'achieved': round(achieved, 2), 'peak': peaks['hbm_gbs'], 'unit': 'GB/s',
                      'frac': round(achieved / peaks['hbm_gbs'], 4),
-                     # ncu on the 1 M-node / degree-48 / F=256 product: 18.08 GB of DRAM traffic for 51.38 M entries x 256
-                     # floats = 1.375 B per (entry x float); scaled here by this run's sum of nnz x F (= flops / 2), per step
+                     # ncu on the 1 M-node / degree-48 / F=256 product: 20.65 GB of DRAM traffic for 51.38 M entries x 256
+                     # floats = 1.57 B per (entry x float); scaled here by this run's sum of nnz x F (= flops / 2), per step
                      'traffic': round(DRAM_BYTES_PER_ENTRY_FLOAT * slow['flops'] / 2 / args.steps),
                      'traffic_source': 'scaled from profiles/k_spmm_rows_v4_rmat1m_deg48_f256.md by nnz x F; per step, all products',
                      'peak_source': peaks['source'],
