@@ -332,7 +332,10 @@ def cpu_sample_inputs(cfg, args, device):
     full = COO_Graph.from_dict(args.config, d, device=device)
     part = full.part_dict(0, CPU_SAMPLE_PARTS)
     n = part['adj'].size(0)
-    return dict(adj=part['adj'].cpu().coalesce(), x=full.features.cpu(), labels=full.labels[:n].cpu(), mask=full.train_mask[:n].cpu(), n=n)
+    a = part['adj'].cpu().coalesce()
+    # the partition pads the column count to CPU_SAMPLE_PARTS * n; the padding columns hold no entry, the features have N rows
+    adj = torch.sparse_coo_tensor(a.indices(), a.values(), (n, full.features.size(0)), is_coalesced=True)
+    return dict(adj=adj, x=full.features.cpu(), labels=full.labels[:n].cpu(), mask=full.train_mask[:n].cpu(), n=n)
 
 
 def time_cpu_sample(inp, cfg, args, steps, warmup=0):

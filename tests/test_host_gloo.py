@@ -221,3 +221,17 @@ def test_compact_peer_loop_bookkeeping_simulated_on_the_host(P):
             z = z + r['blocks'][j] @ area[lay['area_offsets'][j]:lay['area_offsets'][j] + lay['stage_rows'][j]]
         want = sum(A[me][s] @ X[s] for s in range(P))
         assert np.allclose(z, want, rtol=1e-12, atol=1e-12)
+
+
+def test_reference_arm_sample_shapes_with_a_ragged_partition():
+    """bench.py --impl reference on a node count that the 16-way sample partition does not divide: the sampled row block
+    and the feature matrix agree in size and the CPU epoch runs."""
+    import argparse
+    sys.path.insert(0, ROOT)
+    import bench
+    cfg = dict(num_nodes=1003, directed_edges=8000, feat_dim=12, num_classes=5, split=(0.6, 0.2, 0.2), hidden=8, layers=2)
+    args = argparse.Namespace(seed=0, no_permute=False, config='ragged')
+    inp = bench.cpu_sample_inputs(cfg, args, torch.device('cpu'))
+    assert inp['adj'].size(1) == inp['x'].size(0) == 1003 and inp['adj'].size(0) == inp['n'] == 63
+    times, threads = bench.time_cpu_sample(inp, cfg, args, steps=1)
+    assert len(times) == 1 and times[0] > 0 and threads >= 1
