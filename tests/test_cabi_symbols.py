@@ -36,6 +36,17 @@ def test_argument_checks_need_no_gpu():
     assert L.dg_spmm_csr(None, None, None, 1, None, 1, 1, 1.0, 0.0, 0, None, None, None) == -1
     assert L.dg_comm_create(None, 0, 1, ctypes.byref(out)) == -1
     assert L.dg_plan_destroy(None) == 0 and L.dg_comm_destroy(None) == 0
+    # the peer-copy loops and the dense transforms reject missing objects before touching a device
+    assert L.dg_comm_peer_alloc(None, 16, None) == -1 and L.dg_comm_peer_open(None, None) == -1 and L.dg_comm_peer_close(None) == -1
+    assert L.dg_comm_peer_capacity(None) == 0
+    assert L.dg_peer_spmm(None, None, 0, None, None, 0, None, None, None, None, None, 0, 0, None, 0, None) == -1
+    assert L.dg_peer_spmm_packed(None, None, 0, None, None, None, 0, None, None, None, None, 0, None, None, None, None, None, 0, 0, None, 0,
+                                 None) == -1
+    assert L.dg_peer_spmm_packed(None, None, 0, None, None, None, 2, None, None, None, None, 0, None, None, None, None, None, 0, 0, None, 0,
+                                 None) == -1                                           # stages without their offsets
+    assert L.dg_dense_nt_masked(None, 4, None, None, 4, None, 4, 1, 1, 1, 0, None, 0, None) == -1
+    assert L.dg_dense_tn(None, 4, None, 4, None, 4, 1, 1, 1, None, 0, 1, None) == -1
+    assert L.dg_dense_supported(0, 1, 1, 4, 4, None, None, None) == 0 and L.dg_dense_tn_supported(1, 300, 1, 300, 4, None, None) == 0
 
 
 def test_product_modules_do_not_import_the_oracle():
