@@ -29,7 +29,6 @@ def command(verbose=False):
     cmd = ['nvcc', '-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-O3', '-std=c++17',
            '-Xcompiler', '-fPIC,-Wall', '-shared', '-I', os.path.join(ROOT, 'include'), '-I', inc,
            '-L', lib, '-l:libnccl.so.2', '-Xlinker', f'-rpath={lib}', '-o', OUTPUT] + srcs
-    cmd[1:1] = os.environ.get('DG_NVCC_EXTRA', '').split()      # e.g. -DDG_ROWS_MIN_BLOCKS=4 for tuning experiments
     if verbose:
         cmd.insert(1, '-Xptxas=-v')
     return cmd, srcs
@@ -38,7 +37,7 @@ def command(verbose=False):
 def up_to_date(srcs):
     if not os.path.exists(OUTPUT):
         return False
-    deps = srcs + [os.path.join(HERE, 'dg_internal.h'), os.path.join(ROOT, 'include', 'dist_gnn_b200.h'), __file__]
+    deps = srcs + [os.path.join(HERE, 'dg_internal.h'), os.path.join(HERE, 'dg_comm.h'), os.path.join(ROOT, 'include', 'dist_gnn_b200.h'), __file__]
     return all(os.path.getmtime(d) <= os.path.getmtime(OUTPUT) for d in deps)
 
 

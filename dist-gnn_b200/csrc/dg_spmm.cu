@@ -21,21 +21,11 @@
 #include <vector>
 #include "dg_internal.h"
 
-#ifndef DG_ROWS_MIN_BLOCKS
+// Launch shapes, fixed after measurement on B200: 256-thread CTAs, 8 resident per SM (64 warps, <= 32 registers per thread),
+// one gathered row in flight per warp (two or four were slower: 11.9 / 12.2 / 14.5 ms on the benchmark graph at F = 256).
 #define DG_ROWS_MIN_BLOCKS 8
-#endif
-#ifndef DG_ROWS_U_SHIFT
-#define DG_ROWS_U_SHIFT 2
-#endif
-#ifndef DG_V4_MIN_BLOCKS
 #define DG_V4_MIN_BLOCKS 8
-#endif
-#ifndef DG_V4_UNROLL
 #define DG_V4_UNROLL 1
-#endif
-#ifndef DG_V4_MAX_TPL
-#define DG_V4_MAX_TPL 2
-#endif
 
 namespace {
 
@@ -276,82 +266,96 @@ __global__ void __launch_bounds__(256) k_spmm_heavy_finish(const SpmmArgs a)
     }
 }
 
-// ---- lean kernels for the common wide case: 16-byte aligned rows of >= 128 bytes, 32-bit row offsets ----------------------
-// Same scheduling and the same sum order as the generic kernels above, written to need few registers: on B200 the
-// gather runs fastest at full occupancy (64 warps per SM, one or two rows of B in flight per warp) - measured 4.9 ms
-// against 5.6 ms (F = 256, R-MAT 1 M nodes, degree 48) for the generic kernel at 32 warps per SM.
-// Every lane owns TPL float4 of the output row at float4 index lane + 32 t of the column tile; `on[t]` masks the lanes
-// of a partial last tile.  Row offsets col * (ldb / 4) are 32-bit (the host checks k * ldb / 4 < 2^31).
-template <int TPL, int U>
-__device__ __forceinline__ void gather_v4(const float4* __restrict__ bl, int ld4, const int32_t* __restrict__ col,
-                                          const float* __restrict__ val, int64_t e0, int64_t e1, const bool (&on)[TPL],
-                                          int lane, float4 (&acc)[TPL])
+// ---- lean kernel for 16-byte aligned rows: float4 gathers, 32-bit offsets, one launch per product ---------------------
+// Same scheduling and the same sum order as the generic kernels above, written to need few registers: on B200 the gather
+// runs fastest at full occupancy (64 warps per SM, one gathered row per warp in flight).  A warp covers a column tile of
+// 128 floats (every lane one float4; blockIdx.y walks the tiles, tile-major, so the CTAs resident at one time gather from
+// the same 512-byte slice of B's rows), `on` masks the lanes of a partial last tile.  Row offsets col * (ldb / 4) are 32-bit
+// (the host checks k * ldb / 4 < 2^31).  Measured on the 2,449,029-node benchmark graph (F = 256; whole graph / the eight
+// 306 k-row stage blocks of one rank): two float4 per lane in separate row and chunk kernels 12.83 / 2.73 ms, this kernel
+// 12.16 / 2.50 ms; F = 100: 6.15 / 1.82 -> 6.09 / 1.39 ms.
+template <int U>
+__device__ __forceinline__ void gather_v4(const float4* __restrict__ bl, int ld4, const int32_t* __restrict__ colp,
+                                          const float* __restrict__ valp, int len, bool on, float4& acc)
 {
-    for (int64_t e = e0; e < e1; e += 32) {
-        const int cnt = (int)min((int64_t)32, e1 - e);
+    // colp / valp point at this lane's first entry (entry `lane` of the range); len = entries in the range (a light row or
+    // one chunk of a split row, so it fits 32 bits with room to spare)
+    for (int base = 0; base < len; base += 32) {
+        const int cnt = min(32, len - base);
         int c = 0;
         float v = 0.f;
-        if (lane < cnt) {
-            c = __ldcs(col + e + lane) * ld4;
-            v = __ldcs(val + e + lane);
+        if ((int)(threadIdx.x & 31) < cnt) {
+            c = __ldcs(colp + base) * ld4;        // streamed once: keep it from displacing rows of B in cache
+            v = __ldcs(valp + base);
         }
         for (int k = 0; k < cnt; k += U) {
-            float4 x[U][TPL];
+            float4 x[U];
             float w[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int idx = __shfl_sync(0xffffffffu, c, (k + u) & 31);
                 w[u] = __shfl_sync(0xffffffffu, v, (k + u) & 31);     // lanes >= cnt hold 0: a zero weight ...
-                const bool ok = k + u < cnt;
-#pragma unroll
-                for (int t = 0; t < TPL; ++t)                          // ... and nothing is loaded for them
-                    x[u][t] = ok && on[t] ? __ldg(bl + idx + 32 * t) : make_float4(0.f, 0.f, 0.f, 0.f);
+                x[u] = k + u < cnt && on ? __ldg(bl + idx) : make_float4(0.f, 0.f, 0.f, 0.f);   // ... and nothing is loaded
             }
 #pragma unroll
-            for (int u = 0; u < U; ++u)
-#pragma unroll
-                for (int t = 0; t < TPL; ++t) {
-                    acc[t].x = fmaf(w[u], x[u][t].x, acc[t].x); acc[t].y = fmaf(w[u], x[u][t].y, acc[t].y);
-                    acc[t].z = fmaf(w[u], x[u][t].z, acc[t].z); acc[t].w = fmaf(w[u], x[u][t].w, acc[t].w);
-                }
+            for (int u = 0; u < U; ++u) {
+                acc.x = fmaf(w[u], x[u].x, acc.x); acc.y = fmaf(w[u], x[u].y, acc.y);
+                acc.z = fmaf(w[u], x[u].z, acc.z); acc.w = fmaf(w[u], x[u].w, acc.w);
+            }
         }
     }
 }
 
-template <int TPL, int U>
-__global__ void __launch_bounds__(256, DG_V4_MIN_BLOCKS) k_spmm_rows_v4(const SpmmArgs a)
+// One launch for a whole product: the first `chunk_ctas` CTAs take the chunks of the split rows (one warp per chunk, partial
+// sums to scratch), the others the light rows.  A chunk is a chain of `chunk` gathers walked by one warp, so on a small
+// block the chunk work is a fixed latency that does not fill the GPU (385 CTAs for a 306 k-row stage block of the 8-rank
+// partition: 0.09 ms on its own next to 0.25 ms of light rows); issued first in the same grid it runs underneath the light
+// rows instead of after them.  k_spmm_heavy_finish follows as a second launch.
+// PLAIN: alpha == 1 and no row scale, bias or ReLU - what the stage loops run; fmaf(beta, old, sum) with old = 0 is sum, so
+// it gives the bits of the general epilogue.
+template <int U, bool PLAIN>
+__global__ void __launch_bounds__(256, DG_V4_MIN_BLOCKS) k_spmm_v4(const SpmmArgs a, const int chunk_ctas)
 {
     __shared__ int next_row;
     const int lane = threadIdx.x & 31;
-    const int vec0 = blockIdx.y * (32 * TPL) + lane;                  // this lane's first float4 of the row
-    bool on[TPL];
-#pragma unroll
-    for (int t = 0; t < TPL; ++t) on[t] = vec0 + 32 * t < a.nvec;
+    const int vec0 = blockIdx.y * 32 + lane;                          // this lane's float4 of the row
+    const bool on = vec0 < a.nvec;
     const float4* bl = reinterpret_cast<const float4*>(a.B) + vec0;
     const int ld4 = (int)(a.ldb >> 2);
-    const int64_t row0 = (int64_t)blockIdx.x * a.rows_per_cta;
-    const int nrows = (int)min((int64_t)a.rows_per_cta, (int64_t)a.m - row0);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if ((int)blockIdx.x < chunk_ctas) {
+        const int chunk_id = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+        if (chunk_id >= a.n_chunks) return;
+        const dg_chunk ch = a.chunks[chunk_id];
+        gather_v4<U>(bl, ld4, a.col + ch.e0 + lane, a.val + ch.e0 + lane, (int)(ch.e1 - ch.e0), on, acc);
+        if (on) reinterpret_cast<float4*>(a.scratch + (size_t)ch.slot * (size_t)a.F)[vec0] = acc;
+        return;
+    }
+    const int32_t row0 = ((int)blockIdx.x - chunk_ctas) * a.rows_per_cta;     // m < 2^31
+    const int nrows = min(a.rows_per_cta, a.m - row0);
     if (threadIdx.x == 0) next_row = blockDim.x >> 5;
     __syncthreads();
     int r = threadIdx.x >> 5;
     while (r < nrows) {
-        const int32_t i = (int32_t)(row0 + r);
-        const int64_t e0 = __ldg(a.rowptr + i), e1 = __ldg(a.rowptr + i + 1);
-        if (e1 - e0 <= a.heavy_threshold) {
-            float4 acc[TPL];
-#pragma unroll
-            for (int t = 0; t < TPL; ++t) acc[t] = make_float4(0.f, 0.f, 0.f, 0.f);
-            gather_v4<TPL, U>(bl, ld4, a.col, a.val, e0, e1, on, lane, acc);
-            float4* crow = reinterpret_cast<float4*>(a.C + (size_t)i * (size_t)a.ldc) + vec0;
-#pragma unroll
-            for (int t = 0; t < TPL; ++t) {
-                if (!on[t]) continue;
+        const int32_t i = row0 + r;
+        const int64_t e0 = __ldg(a.rowptr + i);
+        const int64_t len = __ldg(a.rowptr + i + 1) - e0;
+        if (len <= a.heavy_threshold) {
+            gather_v4<U>(bl, ld4, a.col + e0 + lane, a.val + e0 + lane, (int)len, on, acc);
+            if (on) {
+                float4* cp = reinterpret_cast<float4*>(a.C + (size_t)i * (size_t)a.ldc) + vec0;
                 float4 old = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (a.beta != 0.f) old = crow[32 * t];
-                const int c = (vec0 + 32 * t) * 4;
-                crow[32 * t] = make_float4(finish(a, acc[t].x, old.x, i, c), finish(a, acc[t].y, old.y, i, c + 1),
-                                           finish(a, acc[t].z, old.z, i, c + 2), finish(a, acc[t].w, old.w, i, c + 3));
+                if (a.beta != 0.f) old = *cp;
+                if constexpr (PLAIN) {
+                    *cp = make_float4(fmaf(a.beta, old.x, acc.x), fmaf(a.beta, old.y, acc.y), fmaf(a.beta, old.z, acc.z),
+                                      fmaf(a.beta, old.w, acc.w));
+                } else {
+                    const int c = vec0 * 4;
+                    *cp = make_float4(finish(a, acc.x, old.x, i, c), finish(a, acc.y, old.y, i, c + 1),
+                                      finish(a, acc.z, old.z, i, c + 2), finish(a, acc.w, old.w, i, c + 3));
+                }
             }
+            acc = make_float4(0.f, 0.f, 0.f, 0.f);
         }
         int nxt = 0;
         if (lane == 0) nxt = atomicAdd(&next_row, 1);
@@ -359,42 +363,21 @@ __global__ void __launch_bounds__(256, DG_V4_MIN_BLOCKS) k_spmm_rows_v4(const Sp
     }
 }
 
-template <int TPL, int U>
-__global__ void __launch_bounds__(256, DG_V4_MIN_BLOCKS) k_spmm_chunks_v4(const SpmmArgs a)
-{
-    const int lane = threadIdx.x & 31;
-    const int chunk_id = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (chunk_id >= a.n_chunks) return;
-    const int vec0 = blockIdx.y * (32 * TPL) + lane;
-    bool on[TPL];
-#pragma unroll
-    for (int t = 0; t < TPL; ++t) on[t] = vec0 + 32 * t < a.nvec;
-    const dg_chunk ch = a.chunks[chunk_id];
-    float4 acc[TPL];
-#pragma unroll
-    for (int t = 0; t < TPL; ++t) acc[t] = make_float4(0.f, 0.f, 0.f, 0.f);
-    gather_v4<TPL, U>(reinterpret_cast<const float4*>(a.B) + vec0, (int)(a.ldb >> 2), a.col, a.val, ch.e0, ch.e1, on, lane, acc);
-    float4* srow = reinterpret_cast<float4*>(a.scratch + (size_t)ch.slot * (size_t)a.F) + vec0;
-#pragma unroll
-    for (int t = 0; t < TPL; ++t)
-        if (on[t]) srow[32 * t] = acc[t];
-}
-
-template <int TPL>
 int launch_v4(const SpmmArgs& a, cudaStream_t stream)
 {
     constexpr int U = DG_V4_UNROLL;
-    const int col_chunks = (a.nvec + 32 * TPL - 1) / (32 * TPL);
-    if (a.m > 0) {
-        dim3 grid((unsigned)(((int64_t)a.m + a.rows_per_cta - 1) / a.rows_per_cta), (unsigned)col_chunks);
-        k_spmm_rows_v4<TPL, U><<<grid, 256, 0, stream>>>(a);
+    const int col_tiles = (a.nvec + 31) / 32;
+    const int chunk_ctas = (a.n_chunks + 7) / 8;
+    const int64_t row_ctas = ((int64_t)a.m + a.rows_per_cta - 1) / a.rows_per_cta;
+    if (chunk_ctas + row_ctas > 0) {
+        dim3 grid((unsigned)(chunk_ctas + row_ctas), (unsigned)col_tiles);
+        if (a.flags == 0u && a.alpha == 1.f) k_spmm_v4<U, true><<<grid, 256, 0, stream>>>(a, chunk_ctas);
+        else k_spmm_v4<U, false><<<grid, 256, 0, stream>>>(a, chunk_ctas);
         g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
     }
-    if (a.n_chunks > 0) {
-        dim3 grid((unsigned)((a.n_chunks + 7) / 8), (unsigned)col_chunks);
-        k_spmm_chunks_v4<TPL, U><<<grid, 256, 0, stream>>>(a);
+    if (a.n_heavy > 0) {
         k_spmm_heavy_finish<<<(unsigned)a.n_heavy, 256, 0, stream>>>(a);
-        g_kernel_launches.fetch_add(2, std::memory_order_relaxed);
+        g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
     }
     return (int)cudaGetLastError();
 }
@@ -402,8 +385,7 @@ int launch_v4(const SpmmArgs& a, cudaStream_t stream)
 template <int VEC, int LPR, int TPL>
 int launch_variant(const SpmmArgs& a, cudaStream_t stream)
 {
-    constexpr int U0 = (TPL * VEC >= 16) ? 2 : (TPL * VEC >= 8) ? 4 : 8;
-    constexpr int U = (U0 >> DG_ROWS_U_SHIFT) > 0 ? (U0 >> DG_ROWS_U_SHIFT) : 1;
+    constexpr int U = (TPL * VEC >= 8) ? 1 : 2;          // gathers in flight per lane group before the first FMA
     const int col_chunks = (a.nvec + LPR * TPL - 1) / (LPR * TPL);
     if (a.m > 0) {
         dim3 grid((unsigned)(((int64_t)a.m + a.rows_per_cta - 1) / a.rows_per_cta), (unsigned)col_chunks);
@@ -422,11 +404,7 @@ int launch_variant(const SpmmArgs& a, cudaStream_t stream)
 template <int VEC>
 int launch_vec(const SpmmArgs& a, cudaStream_t stream)
 {
-    int nvec = a.nvec;
-    // Column tile: at most `cap` vectors of a row per pass over the entries (grid.y walks the tiles, and all CTAs of one
-    // tile are scheduled before the next tile's).  A narrower tile shrinks the slice of B that competes for the L2.
-    static const int cap = [] { const char* e = std::getenv("DG_ROWS_TILE_VECS"); return e && *e ? std::atoi(e) : 0; }();
-    if (cap > 0 && nvec > cap) nvec = cap;
+    const int nvec = a.nvec;
     if (nvec <= 4) return launch_variant<VEC, 4, 1>(a, stream);
     if (nvec <= 8) return launch_variant<VEC, 8, 1>(a, stream);
     if (nvec <= 16) return launch_variant<VEC, 16, 1>(a, stream);
@@ -471,8 +449,11 @@ int dg_spmm_launch_rows(const dg_plan* plan, const float* val, const float* B, i
     if (F % 4 == 0 && ldb % 4 == 0 && ldc % 4 == 0 && aligned(B, 16) && aligned(C, 16)) vec = 4;
     else if (F % 2 == 0 && ldb % 2 == 0 && ldc % 2 == 0 && aligned(B, 8) && aligned(C, 8)) vec = 2;
     a.nvec = F / vec;
-    if (vec == 4 && a.nvec > 16 && (int64_t)plan->k * (ldb / 4) + a.nvec < (int64_t)INT32_MAX)
-        return a.nvec <= 32 || DG_V4_MAX_TPL == 1 ? launch_v4<1>(a, stream) : launch_v4<2>(a, stream);
+    // The lean kernel takes rows of more than 64 floats, and narrower ones (36 to 64 floats) when the rows are short: there
+    // (stage blocks of a partition, about 6 entries per row) it is 18 % faster than the generic kernel, which wins on long
+    // rows by walking two entries per warp at a time (whole graph, F = 48: 4.1 against 4.9 ms).
+    const bool narrow_ok = a.nvec > 8 && plan->nnz < (int64_t)16 * plan->m;
+    if (vec == 4 && (a.nvec > 16 || narrow_ok) && (int64_t)plan->k * (ldb / 4) + a.nvec < (int64_t)INT32_MAX) return launch_v4(a, stream);
     switch (vec) {
         case 4: return launch_vec<4>(a, stream);
         case 2: return launch_vec<2>(a, stream);

@@ -13,9 +13,16 @@
 // written by the chunk kernel before the finishing kernel reads it - so no clearing is done between calls, but two
 // calls that overlap in time on the GPU (different streams) race on it.  Serialise them on one stream.
 //
-// Set-up: the array's name below is a host-side handle, not a device address.  The first call on each device looks the
-// address up once with cudaGetSymbolAddress while that device is current and caches it; that first call may initialise
-// the CUDA module, so make it before starting any stream capture.
+// Set-up: the array's name below is a host-side handle, not a device address.  The address is looked up once per device
+// with cudaGetSymbolAddress while that device is current, and cached.  With CUDA's lazy module loading that first lookup
+// is also the moment the 16 MiB array is materialised on the device (it can fail for lack of memory, and may synchronise).
+// dg_static_scratch_prepare() does the lookup on its own: call it once per device where an allocation is still acceptable
+// (next to dg_plan_create, before the host's pool reserves the rest of the memory, before any stream capture); after it,
+// dg_spmm_csr_static touches neither the allocator nor the module loader.  Without it the first product call on a device
+// does the lookup.
+//
+// The entry always runs the row kernels (the streaming family sizes its scratch differently) and its products are not
+// counted by dg_profile_begin / dg_profile_end.
 #include <mutex>
 #include "dg_internal.h"
 
@@ -45,6 +52,14 @@ int static_scratch_address(int device, float** out)
 }  // namespace
 
 extern "C" int64_t dg_static_scratch_capacity(void) { return DG_STATIC_SCRATCH_FLOATS; }
+
+extern "C" int dg_static_scratch_prepare(void)
+{
+    int device = -1;
+    DG_CUDA(cudaGetDevice(&device));
+    float* unused = nullptr;
+    return static_scratch_address(device, &unused);
+}
 
 extern "C" int dg_spmm_csr_static(const dg_plan* plan, const float* val, const float* B, int64_t ldb, float* C,
                                   int64_t ldc, int32_t F, float alpha, float beta, uint32_t flags,

@@ -200,8 +200,3 @@ class DistEnv:
         if dist.is_initialized():
             dist.destroy_process_group()
         DistEnv.env = None
-
-
-class DistUtil:
-    def __init__(self, env):
-        self.env = env

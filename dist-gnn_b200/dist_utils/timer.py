@@ -29,12 +29,16 @@ class TimerCtx:
             end = torch.cuda.Event(enable_timing=True)
             end.record()
             self.timer.pending.append((self.key, self.begin, end))
+            if len(self.timer.pending) >= self.timer.MAX_PENDING:       # a long run never holds more than this many event pairs
+                self.timer.resolve()
         else:
             self.timer.duration_dict[self.key] += time.time() - self.t0
         self.timer.count_dict[self.key] += 1
 
 
 class DistTimer:
+    MAX_PENDING = 4096
+
     def __init__(self, env):
         self.env = env
         self.start_time_dict = {}
@@ -42,12 +46,17 @@ class DistTimer:
         self.count_dict = defaultdict(int)
         self.pending = []
 
-    def _resolve(self):
+    def resolve(self, synchronize=True):
+        """Adds the elapsed time of the recorded event pairs to their keys.  The training loop calls it with
+        synchronize=False right after it has read the loss (the device is idle then), so the list never grows."""
         if self.pending:
-            torch.cuda.synchronize()
+            if synchronize:
+                torch.cuda.synchronize(self.env.device if self.env.device.type == 'cuda' else None)
             for key, begin, end in self.pending:
                 self.duration_dict[key] += begin.elapsed_time(end) / 1000.0
             self.pending = []
+
+    _resolve = resolve
 
     def timing(self, key):
         return TimerCtx(self, key, cuda=False)

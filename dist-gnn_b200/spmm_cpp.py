@@ -59,6 +59,7 @@ def lib():
             'dg_spmm_csr': ([vp, vp, vp, i64, vp, i64, i32, f32, f32, u32, vp, vp, vp], ctypes.c_int),
             'dg_spmm_csr_static': ([vp, vp, vp, i64, vp, i64, i32, f32, f32, u32, vp, vp, vp], ctypes.c_int),
             'dg_static_scratch_capacity': ([], ctypes.c_int64),
+            'dg_static_scratch_prepare': ([], ctypes.c_int),
             'dg_spmm_coo': ([vp, vp, vp, i64, i32, i32, vp, vp, i32, f32, f32, vp], ctypes.c_int),
             'dg_comm_unique_id': ([ctypes.c_char_p], ctypes.c_int),
             'dg_comm_create': ([ctypes.c_char_p, ctypes.c_int, ctypes.c_int, pp], ctypes.c_int),

@@ -96,11 +96,15 @@ int dg_spmm_csr(const dg_plan* plan, const float* val, const float* B, int64_t l
  * arguments and results to dg_spmm_csr, but the partial sums of split rows go to a fixed 16 MiB array inside the
  * library image (held by every GPU that loads the library, shared by all calls on that GPU).  Returns DG_ERR_SCRATCH
  * when heavy_chunks * F exceeds dg_static_scratch_capacity() floats.  Calls that overlap in time on one GPU race on
- * the array; the first call on a device resolves the array's address and should happen before any stream capture. */
+ * the array.  The array is materialised on a device (16 MiB, by the CUDA module loader) the first time its address is
+ * resolved there: dg_static_scratch_prepare() does that for the current device and is meant to be called once where an
+ * allocation is still acceptable (beside dg_plan_create, before any stream capture); without it the first
+ * dg_spmm_csr_static on a device does it.  Always runs the row kernels; not counted by dg_profile_begin/_end. */
 int dg_spmm_csr_static(const dg_plan* plan, const float* val, const float* B, int64_t ldb, float* C, int64_t ldc,
                        int32_t F, float alpha, float beta, uint32_t epilogue_flags, const float* row_scale,
                        const float* bias, void* stream);
 int64_t dg_static_scratch_capacity(void);
+int dg_static_scratch_prepare(void);
 
 /* ---- drop-in for spmm_cusparse(row, col, val, A_row, A_col, B, C, alpha, beta) (spmm.cpp:17) ----------------------
  * Same nine operands plus the dense width F and the stream; B is k x F and C is m x F, both contiguous.

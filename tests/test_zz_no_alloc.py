@@ -11,7 +11,7 @@ import pytest
 import torch
 
 from conftest import assert_close
-from oracle import ref_graph
+from oracle import ref_gcn, ref_graph
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-5
@@ -42,16 +42,20 @@ def test_static_scratch_entry_matches_the_allocating_entry_twice_in_a_row():
     dev = lambda a, dt=None: torch.from_numpy(np.ascontiguousarray(a)).to('cuda', dtype=dt)
     plan = spmm_cpp.SpmmPlan(dev(A.row, torch.int32), dev(A.col, torch.int32), dev(A.val), 300, 400, heavy_threshold=32, chunk=24)
     assert plan.stats()['heavy_chunks'] > 0                       # the scratch path is what this test is about
+    assert L.dg_static_scratch_prepare() == 0                     # the one step that may touch the module loader
     for width, alpha, beta, flags in ((64, 1.0, 1.0, 0), (47, 0.5, 0.0, 4), (256, 1.25, -0.5, 0)):
-        B = dev(rng.standard_normal((400, width), dtype=np.float32))
-        C0 = dev(rng.standard_normal((300, width), dtype=np.float32))
+        B_host = rng.standard_normal((400, width), dtype=np.float32)
+        C_host = rng.standard_normal((300, width), dtype=np.float32)
+        B, C0 = dev(B_host), dev(C_host)
+        oracle = ref_gcn.spmm_epilogue(A, B_host, C_host, alpha, beta, relu=bool(flags & 4))     # the CPU restatement
         want = C0.clone()
         assert _call(L.dg_spmm_csr, plan, B, want, alpha, beta, flags) == 0
         for attempt in range(2):                                  # the array keeps the previous call's contents
             got = C0.clone()
             assert _call(L.dg_spmm_csr_static, plan, B, got, alpha, beta, flags) == 0
             torch.cuda.synchronize()
-            assert_close(got.cpu().numpy(), want.cpu().numpy(), TOL, f'F={width} call {attempt + 1}')
+            assert_close(got.cpu().numpy(), oracle, TOL, f'F={width} call {attempt + 1} vs the oracle')
+            assert_close(got.cpu().numpy(), want.cpu().numpy(), TOL, f'F={width} call {attempt + 1} vs dg_spmm_csr')
         # a different product in between must not leak into the next one
         other = torch.zeros(300, 8, device='cuda')
         assert _call(L.dg_spmm_csr_static, plan, torch.ones(400, 8, device='cuda'), other, 1.0, 0.0) == 0
