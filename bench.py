@@ -26,7 +26,6 @@ for _p in (ROOT, PKG):
 import torch  # noqa: E402
 
 METRIC, UNIT = 'gcn_epoch_ms', 'ms'
-CPU_SAMPLE_PARTS = 16     # the CPU legs time one rank's share of a 16-way 1D row partition and scale by 16
 DRAM_BYTES_PER_ENTRY_FLOAT = 1.57    # measured DRAM traffic of a product per (stored entry x float of width), see roofline
 
 
@@ -40,13 +39,15 @@ def parse():
     ap.add_argument('--rep', type=int, default=1, help='1.5D replication factor (1 = plain 1D)')
     ap.add_argument('--layers', type=int, default=0, help='override the number of GCN layers')
     ap.add_argument('--seed', type=int, default=0)
-    ap.add_argument('--stage-group', type=int, default=0, help='stages fused into one product (0 = the default of DistEnv)')
+    ap.add_argument('--stage-group', default=None, help='stages fused into one product: a number, or for peer_compact a size list such as 4,2,1 (default: that of DistEnv)')
     ap.add_argument('--stage-order', default=None, choices=['reference', 'local_first', 'feature_chunks', 'peer_copy', 'peer_compact'],
                     help='order of the products inside a distributed SpMM (default: that of DistEnv)')
     ap.add_argument('--chunk-width', type=int, default=0, help='column chunk width of the feature_chunks order (0 = default 64)')
     ap.add_argument('--dense', default=None, choices=['fp32', '3xtf32', 'tcgen05'],
                     help='dense transform: fp32 library GEMM, or three tensor-core TF32 passes with fp32 accumulation')
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--cpu-sample-divisor', type=int, default=16,
+                    help='the CPU legs run a graph with 1/D of the nodes and edges and scale by the stored entries (1 = the full graph)')
     ap.add_argument('--profiler-range', action='store_true',
                     help='cudaProfilerStart/Stop around the device-resident timed steps (for ncu --profile-from-start off)')
     ap.add_argument('--no-permute', action='store_true', help='keep the raw R-MAT vertex order (skewed row blocks)')
@@ -123,8 +124,7 @@ def build_rank_graph(cfg, args, env):
     del d
     parts = env.world_size // env.rep
     g = Parted_COO_Graph.from_full(full, env.rank // env.rep, parts)
-    g.adj = None                      # the stage loop only needs adj_parts; drop the joined copy and the full graph
-    del full
+    del full                          # g.adj (the rank's whole row block) stays: the parity check reads sampled rows of it
     torch.cuda.empty_cache()
     return g
 
@@ -146,7 +146,7 @@ def run_ours(args):
         raise SystemExit(f'--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}')
     if not torch.cuda.is_available():
         raise SystemExit('bench.py (impl ours) needs CUDA devices; there is no CPU path')
-    env = DistEnv(rank, world, 'nccl', rep=args.rep, stage_group=args.stage_group or None, stage_order=args.stage_order)
+    env = DistEnv(rank, world, 'nccl', rep=args.rep, stage_group=args.stage_group, stage_order=args.stage_order)
     if args.chunk_width:
         env.chunk_width = args.chunk_width
     import models.gcn as gcn_module
@@ -189,14 +189,19 @@ def run_ours(args):
         if args.profiler_range:
             torch.cuda.profiler.start()
         ev0.record()
+        marks = [ev0]
         for _ in range(args.steps):
             loss = epoch_step()
+            marks.append(torch.cuda.Event(enable_timing=True))
+            marks[-1].record()
         ev1.record()
         fence()
         if args.profiler_range:
             torch.cuda.profiler.stop()
         prof = spmm_cpp.profile_end()
     ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+    spmm_cpp.check_dense_status()                   # a dense kernel that gave up on a bounded wait voids the run
+    step_ms = [a.elapsed_time(b) for a, b in zip(marks[:-1], marks[1:])]      # this rank's epochs, for the median
     final_loss = float(loss.item())
     # ---- end-to-end leg: host features -> device, epoch, loss back to the host, every step ------------------------------
     # Every step's input is copied from pinned host memory inside the timed region (K copies for K steps) and its loss is
@@ -237,6 +242,9 @@ def run_ours(args):
     if env.col_comm is not None:
         comm_info = measure_stage_loops(env, g, sorted(set(dims)), spmm_cpp)
 
+    # ---- parity of the distributed product with a direct fp64 evaluation of sampled rows (outside every timed region) ----
+    parity = parity_check(env, g, sorted({dims[1], dims[-1]}))
+
     # per-rank product time: report the slowest rank's (it sets the epoch time)
     gathered = env.all_gather_object(prof) if world > 1 else [prof]
     slow = max(gathered, key=lambda p: p['spmm_ms'])
@@ -247,10 +255,10 @@ def run_ours(args):
         'metric': METRIC, 'value': round(ms_total / args.steps, 4), 'unit': UNIT, 'n_gpus': world, 'steps': args.steps,
         'warmup': max(args.warmup, 3), 'ms_per_step': round(ms_total / args.steps, 4), 'higher_is_better': False,
         'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
-        'config': {'workload': describe(cfg, args, world), 'cache': 'inputs larger than L2 (adjacency + operands are GBs per rank); no flush',
-                   'partition': '1d' if args.rep == 1 else f'1.5d(c={args.rep})', 'seed': args.seed,
-                   'vertex_permutation': not args.no_permute, 'final_loss': round(final_loss, 6),
-                   'stage_order': env.stage_order, 'stage_group': env.stage_group, 'dense': gcn_module.DENSE_MODE},
+        'config': config_block(cfg, args, world),
+        'run': {'final_loss': round(final_loss, 6), 'stage_order': env.stage_order, 'stage_group': env.stage_group,
+                'dense': gcn_module.DENSE_MODE, 'ms_per_step_median': round(statistics.median(step_ms), 4),
+                'value_is': 'mean over the K timed epochs (one event pair around all of them), max over ranks'},
         'roofline': {'bound': 'hbm', 'achieved': round(achieved, 2), 'peak': peaks['hbm_gbs'], 'unit': 'GB/s',
                      'frac': round(achieved / peaks['hbm_gbs'], 4),
                      # ncu on the 1 M-node / degree-48 / F=256 product: 20.65 GB of DRAM traffic for 51.38 M entries x 256
@@ -268,13 +276,62 @@ def run_ours(args):
         'gpu_launches': launches,
         'clocks': clocks.summary,
     }
+    line['parity'] = parity
     if comm_info is not None:
         line['comm'] = comm_info
     if world == 1 and rank == 0 and not args.no_cpu_baseline:
-        line['cpu_baseline'] = cpu_baseline_from_device(cfg, args, g_single=g, steps=1)
+        ms_cpu, info = cpu_epoch(cfg, args, steps=1, warmup=1)
+        line['cpu_baseline'] = dict(value=round(ms_cpu, 1), unit=UNIT, **info)
     if rank == 0:
         print(json.dumps(line), flush=True)
     env.shutdown()
+    if not parity['ok']:
+        raise SystemExit(f"parity check failed: {parity}")
+
+
+PARITY_TOL = 1e-5
+PARITY_ROWS = 384
+
+
+def parity_check(env, g, widths):
+    """The distributed product of the active schedule against a direct evaluation that shares nothing with it: every rank
+    draws a seeded operand block, runs  z = sum_s A[rank, s] X_s  through the model's own stage loop (models.gcn.broadcast),
+    gathers all operand blocks with torch.distributed, and recomputes PARITY_ROWS sampled rows of its block of A (the
+    longest row among them) in float64 with plain index arithmetic on the row block's COO entries.  Pins what
+    light_dist_gnn/models/gcn.py:16-30 computes.  Returns the worst relative errors over ranks and widths."""
+    from models.gcn import broadcast
+    dev, n = env.device, g.local_num_nodes
+    idx, val = g.adj.indices(), g.adj.values()
+    row = idx[0].contiguous()
+    gen = torch.Generator(device='cpu').manual_seed(977 + env.rank)
+    counts = torch.bincount(row, minlength=n)
+    sample = torch.cat((torch.randperm(n, generator=gen)[:PARITY_ROWS - 1].to(dev), counts.argmax().view(1))).unique()
+    lo = torch.searchsorted(row, sample)
+    hi = torch.searchsorted(row, sample, right=True)
+    lengths = hi - lo
+    slot = torch.repeat_interleave(torch.arange(sample.numel(), device=dev), lengths)        # entry -> sampled row
+    offsets = torch.arange(int(lengths.sum()), device=dev) - torch.repeat_interleave(lengths.cumsum(0) - lengths, lengths)
+    entries = torch.repeat_interleave(lo, lengths) + offsets
+    cols, vals = idx[1][entries], val[entries].double()
+    worst = {'max_rel': 0.0, 'fro_rel': 0.0}
+    for width in widths:
+        x = torch.randn(n, width, generator=torch.Generator(device='cpu').manual_seed(31 * width + env.rank // env.rep)).to(dev)
+        z = broadcast(g.adj_parts, x, f'parity{width}')
+        x_all = env.all_gather_then_cat(x) if env.world_size > 1 else x
+        want = torch.zeros(sample.numel(), width, dtype=torch.float64, device=dev)
+        for c0 in range(0, entries.numel(), 1 << 20):                                        # bounded temporaries
+            sl = slice(c0, c0 + (1 << 20))
+            want.index_add_(0, slot[sl], vals[sl, None] * x_all[cols[sl]].double())
+        got = z[sample].double()
+        worst['max_rel'] = max(worst['max_rel'], float((got - want).abs().max() / want.abs().max().clamp(min=1e-30)))
+        worst['fro_rel'] = max(worst['fro_rel'], float((got - want).norm() / want.norm().clamp(min=1e-30)))
+    every = env.all_gather_object(worst) if env.world_size > 1 else [worst]
+    out = {'max_rel': max(w['max_rel'] for w in every), 'fro_rel': max(w['fro_rel'] for w in every),
+           'rows': int(sample.numel()) * env.world_size, 'widths': list(widths), 'tolerance': PARITY_TOL,
+           'against': 'float64 evaluation of sampled rows of every rank\'s row block on operands gathered with torch.distributed',
+           'schedule': env.stage_order, 'stage_group': env.stage_group}
+    out['ok'] = bool(out['max_rel'] <= PARITY_TOL and out['fro_rel'] <= PARITY_TOL)
+    return out
 
 
 def measure_stage_loops(env, g, widths, spmm_cpp):
@@ -283,7 +340,7 @@ def measure_stage_loops(env, g, widths, spmm_cpp):
     import torch.distributed as dist
     from models.gcn import group_plans, ordered_products
     stages = env.stages()
-    group = min(env.stage_group, len(stages))
+    group = env.stage_group
     roots = [st.root_in_group for st in stages]
     n = g.local_num_nodes
     out = {'stage_group': group, 'stage_order': env.stage_order}
@@ -324,73 +381,157 @@ def load_peaks():
 
 
 # ------------------------------------------------------------------------------------------------ CPU legs
-def cpu_sample_inputs(cfg, args, device):
-    """Row block 0 of a CPU_SAMPLE_PARTS-way 1D partition of the benchmark graph as CPU tensors, made on the GPU when
-    there is one (seconds) and on the host otherwise (minutes)."""
+REF_DIR = os.path.join(ROOT, 'baseline', '_ref', 'light_dist_gnn')     # unmodified copy made by __graft_entry__.build()
+
+
+def sample_config(cfg, divisor):
+    """The bounded CPU workload: the same generator, widths, classes, split and model, 1/divisor of the nodes and of the
+    directed edges (so the average degree is kept).  The dense operands of the sample are that much smaller than the
+    benchmark's and friendlier to the host's caches, which flatters the CPU side."""
+    small = dict(cfg)
+    small['num_nodes'] = cfg['num_nodes'] // divisor
+    small['directed_edges'] = cfg['directed_edges'] // divisor // 2 * 2
+    return small
+
+
+def config_block(cfg, args, world):
+    """The `config` object, the same in both arms."""
+    return {'workload': describe(cfg, args, world), 'partition': '1d' if args.rep == 1 else f'1.5d(c={args.rep})', 'seed': args.seed,
+            'vertex_permutation': not args.no_permute,
+            'cache': 'inputs larger than L2 (adjacency + operands are GBs per rank); no flush'}
+
+
+def _reference_worker(rank, workdir, parts, name, warmup, steps, threads, port):
+    """One gloo rank of the reference's own training flow on the host cores (child process).  Everything on the timed path
+    is the reference's code: dist_utils.DistEnv, coo_graph.Parted_COO_Graph, dist_train.train -> models.GCN ->
+    DistGCNLayer -> broadcast -> C.addmm_(A, B) (light_dist_gnn/main.py:9-21, dist_train.py:26-45, models/gcn.py:9-53).
+    Outside its files: the rendezvous port, the thread count, and torch.cuda.synchronize made a no-op when the process
+    sees no GPU (the reference's timer calls it unconditionally, dist_utils/timer.py:17-24)."""
+    sys.path[:] = [workdir] + [p for p in sys.path if os.path.abspath(p or '.') not in (PKG, ROOT)]
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(parts))
+    torch.set_num_threads(threads)
+    if not torch.cuda.is_available():
+        torch.cuda.synchronize = lambda *a, **k: None
+    import dist_utils, dist_train                                   # the reference's modules (workdir is first on the path)
+    from coo_graph import Parted_COO_Graph
+    assert os.path.abspath(dist_train.__file__).startswith(os.path.abspath(workdir))
+    env = dist_utils.DistEnv(rank, parts, 'gloo')
+    g = Parted_COO_Graph(name, rank=rank, num_parts=parts, device=env.device)
+    if warmup:
+        dist_train.train(g, env, total_epoch=warmup)
+    before = env.timer.duration_dict['epoch']
+    dist_train.train(g, env, total_epoch=steps)
+    keys = {k: float(v) for k, v in env.timer.duration_dict.items()}
+    with open(os.path.join(workdir, f'result_{rank}.json'), 'w') as f:
+        json.dump({'epoch_s': (env.timer.duration_dict['epoch'] - before) / steps, 'timer': keys, 'device': str(env.device),
+                   'nnz': int(g.adj.values().numel())}, f)
+
+
+def run_reference_files(cfg, args, steps, warmup):
+    """Times the UNMODIFIED reference (baseline/_ref/light_dist_gnn) on the host cores over gloo on the sample workload and
+    scales the epoch time to the benchmark graph by the ratio of stored entries.  Returns (ms per full epoch, info)."""
+    import shutil
+    import socket
+    import tempfile
+    import torch.multiprocessing as mp
     from coo_graph import COO_Graph, synthetic
-    d = synthetic.make_dataset(seed=args.seed, permute=not args.no_permute, device=device, **cfg)
-    full = COO_Graph.from_dict(args.config, d, device=device)
-    part = full.part_dict(0, CPU_SAMPLE_PARTS)
-    n = part['adj'].size(0)
-    a = part['adj'].cpu().coalesce()
-    # the partition pads the column count to CPU_SAMPLE_PARTS * n; the padding columns hold no entry, the features have N rows
-    adj = torch.sparse_coo_tensor(a.indices(), a.values(), (n, full.features.size(0)), is_coalesced=True)
-    return dict(adj=adj, x=full.features.cpu(), labels=full.labels[:n].cpu(), mask=full.train_mask[:n].cpu(), n=n)
+    from coo_graph.parted_coo_graph import GraphCache
+    cores = os.cpu_count() or 1
+    parts = max(1, min(8, cores))
+    if parts == 1:
+        raise RuntimeError('the reference timer needs at least two ranks (statistics.stdev)')
+    threads = max(1, cores // parts)
+    small = sample_config(cfg, max(1, args.cpu_sample_divisor))
+    work = tempfile.mkdtemp(prefix='dg_ref_arm_')
+    try:
+        pkg = os.path.join(work, 'light_dist_gnn')
+        shutil.copytree(REF_DIR, pkg)                              # it writes data/ and logs_P/ beside itself
+        device = 'cuda' if torch.cuda.is_available() else 'cpu'
+        d = synthetic.make_dataset(seed=args.seed, permute=not args.no_permute, device=device, **small)
+        full = COO_Graph.from_dict('bench_sample', d, device=device)
+        nnz_sample = int(full.adj.values().numel())
+        folder = os.path.join(pkg, 'data', f'bench_sample_GCN_{parts}_parts')
+        os.makedirs(folder, exist_ok=True)
+        for r in range(parts):                                     # the reference's part files (same keys, dtypes, layout)
+            part = {k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in full.part_dict(r, parts).items()}
+            GraphCache.save_dict(part, os.path.join(folder, f'part_{r}_of_{parts}.coo_graph'))
+        del d, full
+        with socket.socket() as sock:
+            sock.bind(('127.0.0.1', 0))
+            port = sock.getsockname()[1]
+        saved = {k: os.environ.get(k) for k in ('CUDA_VISIBLE_DEVICES', 'TMPDIR')}
+        os.environ['CUDA_VISIBLE_DEVICES'] = ''                    # host cores only, whatever the box has
+        os.environ['TMPDIR'] = work                                # the reference's FileStore lives in the temp folder
+        try:
+            mp.spawn(_reference_worker, (pkg, parts, 'bench_sample', warmup, steps, threads, port), nprocs=parts, join=True)
+        finally:
+            for k, v in saved.items():
+                if v is None:
+                    os.environ.pop(k, None)
+                else:
+                    os.environ[k] = v
+        results = [json.load(open(os.path.join(pkg, f'result_{r}.json'))) for r in range(parts)]
+    finally:
+        shutil.rmtree(work, ignore_errors=True)
+    nnz_full = cfg['directed_edges'] + cfg['num_nodes']
+    scale = nnz_full / nnz_sample
+    slow = max(results, key=lambda r: r['epoch_s'])
+    info = {'cores': cores, 'kind': 'reference',
+            'sample': (f"unmodified light_dist_gnn (dist_train.train over gloo, {parts} ranks x {threads} thread(s), addmm_ sparse path) on a "
+                       f"seeded R-MAT with 1/{max(1, args.cpu_sample_divisor)} of the nodes and edges ({small['num_nodes']:,} nodes, {nnz_sample:,} stored entries, "
+                       f"same widths and model), mean of {steps} epoch(s) on the slowest rank = {slow['epoch_s'] * 1e3:.1f} ms, "
+                       f"x {scale:.2f} (ratio of stored entries)"),
+            'sample_epoch_ms': round(slow['epoch_s'] * 1e3, 2), 'scale': round(scale, 3),
+            'reference_timer_s': {k: round(v, 3) for k, v in slow['timer'].items()}}
+    return slow['epoch_s'] * 1e3 * scale, info
 
 
-def time_cpu_sample(inp, cfg, args, steps, warmup=0):
-    from coo_graph import synthetic
+def run_port_sample(cfg, args, steps, warmup):
+    """Fallback when the reference's files are not in baseline/_ref: the oracle's torch-CPU epoch (the calls the reference
+    issues on its CPU path) of one rank's share of the sample workload, one process, all host threads."""
+    from coo_graph import COO_Graph, synthetic
     from oracle import ref_gcn
     threads = os.cpu_count() or 1
+    small = sample_config(cfg, max(1, args.cpu_sample_divisor))
+    device = 'cuda' if torch.cuda.is_available() else 'cpu'
+    d = synthetic.make_dataset(seed=args.seed, permute=not args.no_permute, device=device, **small)
+    full = COO_Graph.from_dict('bench_sample', d, device=device)
+    adj = full.adj.cpu().coalesce()
     dims = [cfg['feat_dim']] + [cfg['hidden']] * (cfg['layers'] - 1) + [cfg['num_classes']]
     weights = synthetic.glorot_weights(dims, args.seed)
     times = []
     for i in range(warmup + steps):
-        sec, _ = ref_gcn.cpu_epoch_sample(inp['adj'], inp['x'], inp['labels'], inp['mask'], weights, threads)
+        sec, _ = ref_gcn.cpu_epoch_sample(adj, full.features.cpu(), full.labels.cpu(), full.train_mask.cpu(), weights, threads)
         if i >= warmup:
             times.append(sec)
-    return times, threads
+    scale = (cfg['directed_edges'] + cfg['num_nodes']) / adj.values().numel()
+    ms = sum(times) / len(times) * 1e3
+    info = {'cores': threads, 'kind': 'port',
+            'sample': (f"oracle torch-CPU epoch (addmm_ sparse path + mm + CE + Adam, one process, no communication) on a seeded R-MAT with "
+                       f"1/{max(1, args.cpu_sample_divisor)} of the nodes and edges, mean of {steps} epoch(s) = {ms:.1f} ms, x {scale:.2f}"),
+            'sample_epoch_ms': round(ms, 2), 'scale': round(scale, 3)}
+    return ms * scale, info
 
 
-def cpu_baseline_from_device(cfg, args, g_single, steps):
-    """cpu_baseline leg of the N=1 run: the oracle's torch-CPU epoch on a bounded sample, scaled to a full epoch."""
-    n = (cfg['num_nodes'] + CPU_SAMPLE_PARTS - 1) // CPU_SAMPLE_PARTS
-    A = g_single.adj_parts[0]                          # P = 1: the whole normalised adjacency, on the device
-    idx, val = A.indices(), A.values()
-    hi = int(torch.searchsorted(idx[0].contiguous(), torch.tensor([n], device=idx.device)).item())
-    adj = torch.sparse_coo_tensor(idx[:, :hi].cpu(), val[:hi].cpu(), (n, A.size(1)), is_coalesced=True)
-    inp = dict(adj=adj, x=g_single.features.cpu(), labels=g_single.local_labels[:n].cpu(), mask=g_single.local_train_mask[:n].cpu(), n=n)
-    times, threads = time_cpu_sample(inp, cfg, args, steps)
-    ms = statistics.median(times) * 1e3 * CPU_SAMPLE_PARTS
-    return {'value': round(ms, 1), 'unit': UNIT, 'cores': threads, 'kind': 'port', 'sample': cpu_sample_text(n, cfg, len(times))}
-
-
-def cpu_sample_text(n, cfg, steps):
-    return (f'oracle torch-CPU epoch (addmm_ sparse path + mm + CE + Adam) of rank 0 of a {CPU_SAMPLE_PARTS}-way 1D row partition '
-            f"({n:,} of {cfg['num_nodes']:,} rows, all columns, no communication), median of {steps} run(s), ms x {CPU_SAMPLE_PARTS}")
+def cpu_epoch(cfg, args, steps, warmup):
+    if os.path.isdir(REF_DIR):
+        return run_reference_files(cfg, args, steps, warmup)
+    return run_port_sample(cfg, args, steps, warmup)
 
 
 def run_reference(args):
-    """The reference's CPU path (its torch.sparse addmm_ stage products, dense mm, CE, Adam) on the host cores, through
-    the oracle port: the reference's own files cannot travel to the GPU box."""
-    rank = int(os.environ.get('RANK', 0))
-    if rank != 0:
+    """The reference's CPU implementation of the path on the host cores (rank 0 only under torchrun)."""
+    if int(os.environ.get('RANK', 0)) != 0:
         return
     cfg = workload_config(args)
-    device = 'cuda' if torch.cuda.is_available() else 'cpu'
-    inp = cpu_sample_inputs(cfg, args, device)
-    if device == 'cuda':
-        torch.cuda.empty_cache()
-    steps, warmup = min(args.steps, 3), min(args.warmup, 1)
-    times, threads = time_cpu_sample(inp, cfg, args, steps, warmup)
-    ms = sum(times) / len(times) * 1e3 * CPU_SAMPLE_PARTS
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+    ms, info = cpu_epoch(cfg, args, steps, warmup)
     world = int(os.environ.get('WORLD_SIZE', 1))
     line = {
         'impl': 'reference', 'metric': METRIC, 'value': round(ms, 1), 'unit': UNIT, 'n_gpus': world, 'steps': steps, 'warmup': warmup,
         'ms_per_step': round(ms, 1), 'higher_is_better': False, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32',
-        'data': 'synthetic', 'config': {'workload': describe(cfg, args, world), 'partition': '1d' if args.rep == 1 else f'1.5d(c={args.rep})',
-                                        'seed': args.seed, 'vertex_permutation': not args.no_permute},
-        'cpu_baseline': {'value': round(ms, 1), 'unit': UNIT, 'cores': threads, 'kind': 'port', 'sample': cpu_sample_text(inp['n'], cfg, steps)},
+        'data': 'synthetic', 'config': config_block(cfg, args, world),
+        'cpu_baseline': dict(value=round(ms, 1), unit=UNIT, **info),
         'e2e': {'value': round(ms, 1), 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
         'gpu_launches': 0,
     }

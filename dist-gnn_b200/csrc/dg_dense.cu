@@ -57,9 +57,9 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar)
 {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)      // bounded
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int limit = kWaitLimit)      // bounded
 {
-    for (int i = 0; i < kWaitLimit; ++i) {
+    for (int i = 0; i < limit; ++i) {
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -539,7 +539,7 @@ extern "C" int dg_dense_split(const float* src, float* head, float* tail, int64_
 
 extern "C" int dg_dense_supported(int64_t M, int32_t N, int32_t K, int64_t lda, int64_t ldb, const void* A, const void* Bh, const void* Bt)
 {
-    if (M <= 0 || N <= 0 || K <= 0 || N > 256 || M >= ((int64_t)1 << 31)) return 0;
+    if (M <= 0 || N <= 0 || K <= 0 || M >= ((int64_t)1 << 31)) return 0;
     if (lda % 4 || ldb % 4 || lda < K || ldb < K) return 0;                       // TMA strides are multiples of 16 bytes
     if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(Bh) | reinterpret_cast<uintptr_t>(Bt)) & 15) return 0;
     return encode_tiled() != nullptr;
@@ -558,13 +558,20 @@ extern "C" int dg_dense_nt_masked(const float* A, int64_t lda, const float* Bt_h
     if (!A || !Bt_head || !Bt_tail || !C) return DG_ERR_NULL;
     if (ldc < N || (mask && ldm < N)) return DG_ERR_DIMS;
     if (!dg_dense_supported(M, N, K, lda, ldb, A, Bt_head, Bt_tail)) return DG_ERR_UNSUPPORTED;
+    if (N > 256) {      // a result wider than one accumulator: panels of 256 columns, A is streamed once per panel
+        for (int32_t n0 = 0; n0 < N; n0 += 256) {
+            const int rc = dg_dense_nt_masked(A, lda, Bt_head + (int64_t)n0 * ldb, Bt_tail + (int64_t)n0 * ldb, ldb, C + n0, ldc, M,
+                                              N - n0 < 256 ? N - n0 : 256, K, relu, mask ? mask + n0 : nullptr, ldm, stream);
+            if (rc) return rc;
+        }
+        return DG_OK;
+    }
     DenseArgs a{};
     a.C = C; a.ldc = ldc; a.M = M; a.N = N; a.K = K; a.n_pad = (N + 15) / 16 * 16; a.relu = relu ? 1u : 0u;
     a.mask = mask; a.ldm = ldm;
     // Measured: the tensor cores ignore the low 13 bits of a TF32 operand (results with and without the masked head copy are
     // bit-identical), so the tile as loaded serves as head; issuing the head passes before the split is 4 % faster.
-    static const int raw_env = [] { const char* v = getenv("DG_DENSE_RAW_HEAD"); return v ? atoi(v) : 2; }();
-    a.raw_head = raw_env;
+    a.raw_head = 2;
     a.status = dense_status_word();
     if (!a.status) return DG_ERR_STATE;
     CUtensorMap tmA, tmBh, tmBt;
@@ -574,11 +581,10 @@ extern "C" int dg_dense_nt_masked(const float* A, int64_t lda, const float* Bt_h
         return rc;
     const size_t smem = (size_t)STAGES * (2 * BM * 128 + 2 * a.n_pad * 128) + 24 * STAGES + 48 + 1024;
     const int n_tiles = (int)((M + BM - 1) / BM);
-    // two kernels: one tile per CTA, or one persistent CTA per SM walking the tiles (DG_DENSE_NT=tile|persistent forces one)
+    // two kernels: one tile per CTA, or one persistent CTA per SM walking the tiles
     // Narrow results leave room for two one-tile CTAs per SM, which overlap each other's load latency better than the
     // persistent CTA's two stages do (2,449,029 x 256 -> 47: 1.09 ms against 1.28 ms; -> 256: 2.16 against 1.88).
-    static const int forced = [] { const char* v = getenv("DG_DENSE_NT"); return !v ? 0 : !strcmp(v, "tile") ? 1 : !strcmp(v, "persistent") ? 2 : 0; }();
-    const bool per_tile = forced == 1 || (forced == 0 && a.n_pad <= 128);
+    const bool per_tile = a.n_pad <= 128;
     if (per_tile) {
         DG_CUDA(cudaFuncSetAttribute(k_dense_nt, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         k_dense_nt<<<(unsigned)n_tiles, kThreads, smem, (cudaStream_t)stream>>>(tmA, tmBh, tmBt, a);
@@ -600,6 +606,61 @@ extern "C" int dg_dense_status(int* host_status, void* stream)
     DG_CUDA(cudaMemcpyAsync(host_status, w, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     DG_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     return DG_OK;
+}
+
+extern "C" int dg_dense_status_reset(void* stream)
+{
+    int* w = dense_status_word();
+    if (!w) return DG_ERR_STATE;
+    DG_CUDA(cudaMemsetAsync(w, 0, sizeof(int), (cudaStream_t)stream));
+    return DG_OK;
+}
+
+// Self-test of the give-up path every dense kernel shares: a CTA allocates tensor-memory columns as the kernels do, then
+// waits - with a limit of a few thousand polls - on an mbarrier that nothing ever arrives at.  The wait runs out, the
+// thread records it in `flag`, the CTA frees its tensor memory and the kernel returns normally.  Nothing traps or spins
+// without bound; the context stays usable, which the caller can check by running a product afterwards.
+namespace {
+__global__ void __launch_bounds__(64, 1) k_dense_wait_selftest(int* flag, int limit)
+{
+    __shared__ __align__(8) unsigned long long bar_storage;
+    __shared__ uint32_t tmem_slot;
+    const uint32_t bar = smem_u32(&bar_storage);
+    const int warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(32) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmem_slot;
+    if (threadIdx.x == 0 && !mbar_wait(bar, 0, limit)) atomicExch(flag, 1);      // nobody arrives: the wait must give up
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(32) : "memory");
+}
+}  // namespace
+
+extern "C" int dg_dense_wait_selftest(int* host_gave_up, void* stream)
+{
+    if (!host_gave_up) return DG_ERR_NULL;
+    int* flag = nullptr;
+    DG_CUDA(cudaMalloc((void**)&flag, sizeof(int)));
+    cudaError_t e = cudaMemsetAsync(flag, 0, sizeof(int), (cudaStream_t)stream);
+    if (e == cudaSuccess) {
+        k_dense_wait_selftest<<<1, 64, 0, (cudaStream_t)stream>>>(flag, 4096);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(host_gave_up, flag, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    cudaFree(flag);
+    return (int)e;
 }
 
 // ---- weight-gradient product  D[Km x Nn] = X[n x Km]^T * G[n x Nn]  (models/gcn.py:50) -------------------------------------
@@ -870,7 +931,7 @@ int make_map_box(CUtensorMap* map, const float* ptr, int64_t rows, int64_t cols,
 
 extern "C" int dg_dense_tn_supported(int64_t n, int32_t Km, int32_t Nn, int64_t ldx, int64_t ldg, const void* X, const void* G)
 {
-    if (n <= 0 || Km <= 0 || Nn <= 0 || Km > 256 || Nn > 256 || n >= ((int64_t)1 << 31)) return 0;
+    if (n <= 0 || Km <= 0 || Nn <= 0 || n >= ((int64_t)1 << 31)) return 0;
     if (ldx % 4 || ldg % 4 || ldx < Km || ldg < Nn) return 0;
     if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(G)) & 15) return 0;
     return encode_tiled() != nullptr;
@@ -882,6 +943,15 @@ extern "C" int dg_dense_tn(const float* X, int64_t ldx, const float* G, int64_t 
     if (!X || !G || !D || !scratch) return DG_ERR_NULL;
     if (ldd < Nn || max_ctas < 1 || (reinterpret_cast<uintptr_t>(scratch) & 15)) return DG_ERR_DIMS;
     if (!dg_dense_tn_supported(n, Km, Nn, ldx, ldg, X, G)) return DG_ERR_UNSUPPORTED;
+    if (Km > 256 || Nn > 256) {     // wider than two accumulators: 256 x 256 panels of D, one after the other on the stream
+        for (int32_t m0 = 0; m0 < Km; m0 += 256)                  // (they share `scratch`; the operands are streamed once per panel)
+            for (int32_t c0 = 0; c0 < Nn; c0 += 256) {
+                const int rc = dg_dense_tn(X + m0, ldx, G + c0, ldg, D + (int64_t)m0 * ldd + c0, ldd, n, Km - m0 < 256 ? Km - m0 : 256,
+                                           Nn - c0 < 256 ? Nn - c0 : 256, scratch, scratch_floats, max_ctas, stream);
+                if (rc) return rc;
+            }
+        return DG_OK;
+    }
     DenseTnArgs a{};
     a.n = n; a.Km = Km; a.Nn = Nn; a.n_pad = (Nn + 15) / 16 * 16; a.m_halves = Km > 128 ? 2 : 1;
     const int64_t slabs = (n + TN_ROWS - 1) / TN_ROWS;
@@ -889,11 +959,8 @@ extern "C" int dg_dense_tn(const float* X, int64_t ldx, const float* G, int64_t 
     a.rows_per_cta = (slabs + ctas - 1) / ctas * TN_ROWS;
     const int64_t slots = (int64_t)a.m_halves * 128 * a.n_pad;    // one CTA's partial, padding included
     if (ctas * slots > scratch_floats) return DG_ERR_SCRATCH;
-    static const int flush_env = [] { const char* v = getenv("DG_DENSE_TN_FLUSH"); return v ? atoi(v) : 0; }();
-    // 1: no masked head copies (bit-identical results, fewer shared-memory writes); 2 (head x head before the split) is not faster here
-    static const int raw_env = [] { const char* v = getenv("DG_DENSE_RAW_HEAD"); return v ? atoi(v) : 1; }();
-    a.raw_head = raw_env;
-    a.flush_slabs = flush_env > 0 ? flush_env : 16;               // 256 rows = 96 tensor-core accumulations per chain
+    a.raw_head = 1;     // no masked head copies (bit-identical results, fewer shared-memory writes); issuing head x head before the split is not faster here
+    a.flush_slabs = 16;                                           // 256 rows = 96 tensor-core accumulations per chain
     a.partial = scratch;
     a.status = dense_status_word();
     if (!a.status) return DG_ERR_STATE;

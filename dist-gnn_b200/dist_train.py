@@ -3,6 +3,8 @@ import numpy as np
 import torch
 import torch.nn as nn
 
+import spmm_cpp
+
 from coo_graph import Parted_COO_Graph
 from dist_utils import DistEnv
 from models import GCN
@@ -45,6 +47,9 @@ def train(g, env, total_epoch, hidden_dim=256, num_layers=3, weights=None, log_e
             loss.backward()
             optimizer.step()
             losses.append(loss.item())
+            if outputs.is_cuda:         # the device is idle after loss.item(): the cheapest place for both
+                spmm_cpp.check_dense_status()
+                env.timer.resolve(synchronize=False)
             env.logger.log('Epoch {:05d} | Loss {:.4f}'.format(epoch, losses[-1]), rank=0)
         if epoch % log_every == 0 or epoch == total_epoch - 1:
             all_outputs = env.all_gather_then_cat(outputs)

@@ -55,7 +55,9 @@ class DistEnv:
         # rows per product and one read-modify-write of z instead of P-1, while the second half travels under the first.
         chosen = stage_group if stage_group is not None else os.environ.get('DIST_GNN_STAGE_GROUP')
         if chosen is not None:
-            self.stage_group = max(1, int(chosen))
+            # an integer, or for 'peer_compact' a list of group sizes such as "4,2,1" (arrivals per product, in pull order)
+            sizes = [max(1, int(v)) for v in str(chosen).replace('(', '').replace(')', '').replace('[', '').replace(']', '').split(',') if v.strip()]
+            self.stage_group = sizes[0] if len(sizes) == 1 else tuple(sizes)
         elif self.stage_order == 'reference' and rep == 1:
             self.stage_group = max(1, (len(self.stages()) + 1) // 2)
         else:
@@ -65,6 +67,11 @@ class DistEnv:
 
     def __repr__(self):
         return '<DistEnv %d/%d %s>' % (self.rank, self.world_size, self.backend)
+
+    @property
+    def group_k(self):
+        """stage_group as one number, for the loops that fuse a fixed count of stages (a size list is 'peer_compact' only)."""
+        return self.stage_group if isinstance(self.stage_group, int) else self.stage_group[0]
 
     def init_device(self):
         if torch.cuda.is_available() and self.backend == 'nccl':

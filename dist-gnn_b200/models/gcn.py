@@ -29,7 +29,7 @@ def spmm(A, B, C):
 #   'fp32'    plain fp32 library GEMM (CUDA cores), bit-for-bit what the reference's torch.mm does on a GPU
 #   'tcgen05' the library's own tensor-core kernel (dg_dense_nt): three TF32 passes on head/tail splits, fp32 accumulator
 #             in tensor memory, the tall operands split inside the kernel (dg_dense_nt for Z*W and AG*W^T, dg_dense_tn
-#             for the weight gradient X^T*AG); shapes it does not take (odd row strides such as 47) use the library GEMM
+#             for the weight gradient X^T*AG; results wider than 256 in panels, odd row strides on padded copies)
 #   '3xtf32'  each fp32 operand is cut into a TF32-exact head and its residual, and the product is accumulated in fp32
 #             from three tensor-core TF32 GEMMs  head*head + head*tail + tail*head  (the tail*tail term, 2^-22 relative,
 #             is dropped).  About 5e-7 relative error per product - inside the 1e-5 parity bound - at a fraction of the
@@ -39,11 +39,28 @@ PAD_ODD_WIDTHS = os.environ.get('DIST_GNN_PAD_WIDTHS', '1') != '0'
 FUSE_RELU = os.environ.get('DIST_GNN_FUSE_RELU', '1') != '0'
 
 
-def _rows(t):
-    """t itself when its rows are dense and start on 16-byte boundaries (a column slice of a padded buffer), else a copy."""
+_padded_rows = {}
+
+
+def _rows(t, keep=False):
+    """t itself when its rows are dense and start on 16-byte boundaries (a column slice of a padded buffer is fine), else
+    the first t.size(1) columns of a copy whose rows are padded to a multiple of 4 floats.  keep=True caches that copy for
+    as long as t lives and is not modified in place (the input features: 602 floats per row -> 604)."""
     if t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 4 == 0 and t.stride(0) >= t.size(1) and t.data_ptr() % 16 == 0:
         return t
-    return t.contiguous()
+    if keep:
+        hit = _padded_rows.get(id(t))
+        if hit is not None and hit[0]() is t and hit[1] == t._version:
+            return hit[2]
+    rows, cols = t.shape
+    wide = torch.zeros((rows, cols + (-cols) % 4), dtype=t.dtype, device=t.device)
+    wide[:, :cols] = t
+    view = wide[:, :cols]
+    if keep:
+        import weakref
+        key = id(t)
+        _padded_rows[key] = (weakref.ref(t, lambda _r, key=key: _padded_rows.pop(key, None)), t._version, view)
+    return view
 
 
 def _tf32_split(x):
@@ -51,18 +68,20 @@ def _tf32_split(x):
     return head, x - head
 
 
-def dense_mm(a, b, ta=False, tb=False, relu=False, mask=None):
-    """op(a) @ op(b) for fp32 CUDA matrices according to DENSE_MODE; ta / tb transpose the (contiguous) operand.
+def dense_mm(a, b, ta=False, tb=False, relu=False, mask=None, weight_key=None, constant_a=False):
+    """op(a) @ op(b) for fp32 CUDA matrices according to DENSE_MODE; ta / tb transpose the operand.
     relu applies max(x, 0) to the product; mask (same shape as the product) zeroes it where mask <= 0.  Both are fused
-    into the tensor-core kernel's epilogue and are separate passes on the library paths."""
+    into the tensor-core kernel's epilogue and are separate passes on the library paths.  weight_key: the weight object
+    behind b, which lets the tensor-core path keep its transposed, split copy until the weight changes; constant_a: a is
+    an input that never changes (its padded copy, if it needs one, is kept)."""
     if DENSE_MODE == 'tcgen05' and a.is_cuda and not ta:
-        # hand-written tensor-core kernel: a [M x K] times a small matrix given as bt [N x K]; other shapes fall through
-        out = spmm_cpp.dense_nt(_rows(a), b.contiguous() if tb else b.t().contiguous(), relu=relu,
-                                mask=_rows(mask) if mask is not None else None)
+        # hand-written tensor-core kernel: a [M x K] times a small matrix; shapes it does not take fall through
+        out = spmm_cpp.dense_nt(_rows(a), b, transposed=not tb, relu=relu, mask=_rows(mask) if mask is not None else None,
+                                cache_key=weight_key)
         if out is not None:
             return out
     if DENSE_MODE == 'tcgen05' and a.is_cuda and ta and not tb and not relu and mask is None:
-        out = spmm_cpp.dense_tn(_rows(a), _rows(b))                  # a^T @ b with the reduction over the shared rows
+        out = spmm_cpp.dense_tn(_rows(a, keep=constant_a), _rows(b))         # a^T @ b with the reduction over the shared rows
         if out is not None:
             return out
     out = _library_mm(a, b, ta, tb)
@@ -134,7 +153,8 @@ def _stage_loop(env, local_adj_parts, x, z, stages, comm, timed=False):
             area = env.recv_buffers(max(ex['area_rows'], 1), width, nbuf=1, tag='compact')[0]
             landing = [None] * len(ex['own']) + [area[o:o + r] for o, r in zip(ex['area_offsets'], ex['stage_rows'])]
             products = [(spmm_cpp.plan_for(local_adj_parts[stages[i].part]), x, -1) for i in ex['own']]
-            products += [(plan, block, len(ex['own']) + j) for j, (plan, block) in enumerate(zip(ex['plans'], landing[len(ex['own']):]))]
+            products += [(plan, area[o:o + r], len(ex['own']) + last)
+                         for plan, (o, r), last in zip(ex['plans'], ex['plan_slices'], ex['plan_last'])]
             zeros = [0] * len(ex['own'])
             with env.timer.timing_cuda('broadcast+spmm'):
                 spmm_cpp.peer_spmm_packed(comm, ex['packs'], ex['roots'], zeros + ex['stage_offsets'], zeros + ex['stage_rows'], landing,
@@ -148,9 +168,9 @@ def _stage_loop(env, local_adj_parts, x, z, stages, comm, timed=False):
     if comm is not None and env.stage_order == 'local_first':
         with env.timer.timing_cuda('broadcast+spmm'):
             spmm_cpp.bcast_spmm_ordered(comm, *ordered_products(env, local_adj_parts, stages, x), x, z,
-                                        row_comm=env.row_comm, bcast_group=env.stage_group, timed=timed)
+                                        row_comm=env.row_comm, bcast_group=env.group_k, timed=timed)
         return z
-    group = min(env.stage_group, len(stages)) if comm is not None else 1
+    group = min(env.group_k, len(stages)) if comm is not None else 1
     plans = group_plans(local_adj_parts, [st.part for st in stages], group)
     recv = env.recv_buffers(n * group, width) if comm is not None else None
     with env.timer.timing_cuda('broadcast+spmm'):
@@ -162,39 +182,75 @@ def _stage_loop(env, local_adj_parts, x, z, stages, comm, timed=False):
 _compact_cache = {}
 
 
+def group_sizes(count, spec):
+    """How `count` remote arrivals are shared out over the products of a 'peer_compact' loop.  spec: an int k (groups of k,
+    the last one takes what is left) or a sequence of sizes (used in order, the last size repeats)."""
+    if isinstance(spec, int):
+        spec = [spec]
+    spec = [max(1, int(v)) for v in spec] or [1]
+    sizes, i = [], 0
+    while count > 0:
+        take = min(count, spec[min(i, len(spec) - 1)])
+        sizes.append(take)
+        count -= take
+        i += 1
+    return sizes
+
+
 def compact_exchange(env, adj_parts, stages):
     """One-off set-up of the 'peer_compact' stage order for this rank's blocks (1D).  For every remote block: the sorted
-    list of the columns it touches, a plan whose column ids are positions in that list, and - after one exchange of the
-    lists - where this rank's rows start inside each owner's send buffer and which rows this rank packs for every
-    reader.  Collective over the column communicator's ranks (an all-gather of the lists as host objects)."""
+    list of the columns it touches and the block with its column ids replaced by positions in that list; after one
+    exchange of the lists, where this rank's rows start inside each owner's send buffer and which rows this rank packs
+    for every reader.  The pulled lists land side by side in one area in pull order, and env.stage_group consecutive
+    arrivals are multiplied by ONE product over their joined block (column id = position inside the group's slice of the
+    area): fewer read-modify-write passes over the result and longer rows, at the price of waiting for the group's last
+    arrival.  Collective over the column communicator's ranks (an all-gather of the lists as host objects)."""
     import torch.distributed as dist
-    hit = _compact_cache.get(id(adj_parts))
+    key = (id(adj_parts), tuple(group_sizes(len(stages), env.stage_group)))
+    hit = _compact_cache.get(key)
     if hit is not None and hit[0] is adj_parts:
         return hit[1]
     comm = env.col_comm
     me, size = comm.rank, comm.size
     own, remote = schedule.pull_order(stages, me, size)
     n = adj_parts[0].size(0)
-    wanted, plans, kept = {}, [], []
+    wanted, blocks, kept = {}, [], []
     for i in remote:
         block = adj_parts[stages[i].part]
         idx = block.indices()
         if idx.size(1) == 0:
             continue                                                  # an empty block adds nothing: no list, no copy, no product
         touched = torch.unique(idx[1])                                # ascending
-        position = torch.searchsorted(touched, idx[1].contiguous())
-        plans.append(spmm_cpp.SpmmPlan(idx[0].to(torch.int32), position.to(torch.int32).contiguous(), block.values().contiguous(),
-                                       n, touched.numel()))
+        blocks.append((idx[0], torch.searchsorted(touched, idx[1].contiguous()), block.values(), touched.numel()))
         wanted[stages[i].root_in_group] = touched.to(torch.int32).cpu().numpy()
         kept.append(i)
     gathered = [None] * size
     dist.all_gather_object(gathered, wanted, group=env.world_group)   # gathered[q][s]: rows of block s that reader q needs
     lay = schedule.compact_layout(gathered, me, [stages[i].root_in_group for i in kept])
     packs = [(torch.from_numpy(gathered[q][me]).to(env.device), offset) for q, offset in lay['packs']]
-    ex = dict(own=own, remote=kept, plans=plans, packs=packs, roots=[stages[i].root_in_group for i in own + kept],
+    plans, plan_slices, plan_last = [], [], []
+    first = 0
+    for count in group_sizes(len(kept), env.stage_group):
+        members = range(first, first + count)
+        base = lay['area_offsets'][first]
+        rows_total = sum(lay['stage_rows'][j] for j in members)
+        if count == 1:
+            row, col, val, _ = blocks[first]
+        else:
+            row = torch.cat([blocks[j][0] for j in members])
+            col = torch.cat([blocks[j][1] + (lay['area_offsets'][j] - base) for j in members])
+            val = torch.cat([blocks[j][2] for j in members])
+            order = torch.sort(row * rows_total + col).indices        # row-major, inside a row ascending (arrival, column)
+            row, col, val = row[order], col[order], val[order]
+        plans.append(spmm_cpp.SpmmPlan(row.to(torch.int32), col.to(torch.int32).contiguous(), val.contiguous(), n, rows_total))
+        plan_slices.append((base, rows_total))
+        plan_last.append(first + count - 1)
+        first += count
+    ex = dict(own=own, remote=kept, plans=plans, plan_slices=plan_slices, plan_last=plan_last, packs=packs,
+              roots=[stages[i].root_in_group for i in own + kept],
               stage_rows=lay['stage_rows'], stage_offsets=lay['stage_offsets'], area_offsets=lay['area_offsets'],
               area_rows=lay['area_rows'], send_rows=lay['send_rows'], sizes=lay['sizes'])
-    _compact_cache[id(adj_parts)] = (adj_parts, ex)
+    _compact_cache[key] = (adj_parts, ex)
     return ex
 
 
@@ -219,7 +275,7 @@ def ordered_products(env, adj_parts, stages, x, rotate=False):
     for pos, i in enumerate(remote):
         landing[position[i]] = area[pos * n:(pos + 1) * n]
     products = [(spmm_cpp.plan_for(adj_parts[stages[i].part]), x, -1) for i in own]
-    group = max(1, min(env.stage_group, len(remote)))
+    group = max(1, min(env.group_k, len(remote)))
     plans = group_plans(adj_parts, [stages[i].part for i in remote], group) if remote else []
     for g, plan in enumerate(plans):
         members = remote[g * group:(g + 1) * group]
@@ -271,9 +327,10 @@ class DistGCNLayer(torch.autograd.Function):
     def forward(ctx, features, weight, adj_parts, tag, relu=False, input_is_relu=False):
         ctx.save_for_backward(features, weight)
         ctx.adj_parts, ctx.tag, ctx.input_is_relu = adj_parts, tag, input_is_relu
+        ctx.weight_key = weight                      # the caller's tensor object: key of the split-weight cache
         z_local = broadcast(adj_parts, features, 'Forward' + tag)
         with DistEnv.env.timer.timing_cuda('mm'):
-            z_local = dense_mm(z_local, weight, relu=relu)
+            z_local = dense_mm(z_local, weight, relu=relu, weight_key=weight)
         return z_local
 
     @staticmethod
@@ -283,8 +340,8 @@ class DistGCNLayer(torch.autograd.Function):
         with DistEnv.env.timer.timing_cuda('mm'):
             grad_features = None
             if ctx.needs_input_grad[0]:
-                grad_features = dense_mm(ag, weight, tb=True, mask=features if ctx.input_is_relu else None)
-            grad_weight = dense_mm(features, ag, ta=True)
+                grad_features = dense_mm(ag, weight, tb=True, mask=features if ctx.input_is_relu else None, weight_key=ctx.weight_key)
+            grad_weight = dense_mm(features, ag, ta=True, constant_a=not ctx.needs_input_grad[0])
         with DistEnv.env.timer.timing_cuda('all_reduce'):
             DistEnv.env.all_reduce_sum(grad_weight)
         return grad_features, grad_weight, None, None, None, None

@@ -87,6 +87,8 @@ def lib():
             'dg_dense_tn_supported': ([i64, i32, i32, i64, i64, vp, vp], ctypes.c_int),
             'dg_dense_tn': ([vp, i64, vp, i64, vp, i64, i64, i32, i32, vp, i64, i32, vp], ctypes.c_int),
             'dg_dense_status': ([ctypes.POINTER(ctypes.c_int), vp], ctypes.c_int),
+            'dg_dense_status_reset': ([vp], ctypes.c_int),
+            'dg_dense_wait_selftest': ([ctypes.POINTER(ctypes.c_int), vp], ctypes.c_int),
             'dg_profile_begin': ([], ctypes.c_int),
             'dg_profile_end': ([ctypes.POINTER(Profile)], ctypes.c_int),
         }
@@ -474,29 +476,57 @@ def dense_split(w):
     return head, tail
 
 
-def dense_nt(a, bt, relu=False, mask=None):
-    """a [M x K] @ bt[N x K]^T on the tensor cores with fp32 accuracy (dg_dense_nt), or None when the shapes or strides
-    are outside what the kernel takes (the caller then uses a library GEMM).  relu applies max(x, 0) on the way out;
-    mask [M x N] zeroes the result where mask <= 0 (the backward of a ReLU whose output is `mask`)."""
-    lda = _row_major(a, 'a')
-    ldm = _row_major(mask, 'mask') if mask is not None else 0
-    if mask is not None and tuple(mask.shape) != (a.size(0), bt.size(0)):
-        raise RuntimeError(f'mask is {tuple(mask.shape)}, the product {(a.size(0), bt.size(0))}')
-    _dev_tensor(bt, torch.float32, 'bt')
-    M, K = a.shape
-    N = bt.size(0)
-    if bt.size(1) != K:
-        raise RuntimeError(f'inner dimensions differ: {tuple(a.shape)} x {tuple(bt.shape)}^T')
-    if K % 4:                       # the small operand is re-laid with a row stride the tensor maps accept; K itself stays
-        wide = torch.zeros((N, K + (-K) % 4), dtype=torch.float32, device=bt.device)
+_split_cache = {}       # id(weight object) -> (weak reference to it, {transposed flag: (version, head, tail)})
+
+
+def split_operand(w, transposed, cache_key=None):
+    """The small operand of dense_nt, laid out [N x K] (rows padded to a multiple of 4 floats) and split into TF32 head
+    and tail.  transposed=True takes w as [K x N] and transposes it.  With cache_key (the weight object the caller holds,
+    e.g. the nn.Parameter) the result is kept until that tensor is modified in place - its version counter moves with every
+    optimiser step - so a weight is transposed and split once per step, not once per product."""
+    if cache_key is not None:
+        import weakref
+        ident = id(cache_key)
+        entry = _split_cache.get(ident)
+        if entry is None or entry[0]() is not cache_key:       # tensors compare element-wise, so the table is keyed by identity
+            entry = _split_cache[ident] = (weakref.ref(cache_key, lambda _r, ident=ident: _split_cache.pop(ident, None)), {})
+        slot = entry[1]
+        hit = slot.get(transposed)
+        if hit is not None and hit[0] == cache_key._version and hit[1].device == w.device:
+            return hit[1], hit[2]
+    bt = w.detach().t() if transposed else w.detach()
+    N, K = bt.shape
+    if K % 4 or not bt.is_contiguous():
+        wide = torch.zeros((N, K + (-K) % 4), dtype=torch.float32, device=w.device)
         wide[:, :K] = bt
         bt = wide
-    ldb = bt.size(1)
-    if M == 0 or not lib().dg_dense_supported(M, N, K, lda, ldb, a.data_ptr(), bt.data_ptr(), bt.data_ptr()):
-        return None
-    global dense_launches
     head, tail = dense_split(bt)
-    dense_launches += 1
+    if cache_key is not None:
+        slot[transposed] = (cache_key._version, head, tail)
+    return head, tail
+
+
+def dense_nt(a, b, transposed=False, relu=False, mask=None, cache_key=None):
+    """a [M x K] @ op(b) on the tensor cores with fp32 accuracy (dg_dense_nt): b is the small operand, [N x K] as given
+    or [K x N] with transposed=True.  Returns None when the shapes or strides are outside what the kernel takes (the
+    caller then uses a library GEMM).  relu applies max(x, 0) on the way out; mask [M x N] zeroes the result where
+    mask <= 0 (the backward of a ReLU whose output is `mask`); cache_key: see split_operand."""
+    lda = _row_major(a, 'a')
+    if not (isinstance(b, torch.Tensor) and b.is_cuda and b.dtype == torch.float32 and b.dim() == 2):
+        raise RuntimeError('b must be a 2-D fp32 CUDA tensor: this library has no CPU path')
+    M, K = a.shape
+    N = b.size(1) if transposed else b.size(0)
+    if (b.size(0) if transposed else b.size(1)) != K:
+        raise RuntimeError(f'inner dimensions differ: {tuple(a.shape)} x {tuple(b.shape)}{"" if transposed else "^T"}')
+    ldm = _row_major(mask, 'mask') if mask is not None else 0
+    if mask is not None and tuple(mask.shape) != (M, N):
+        raise RuntimeError(f'mask is {tuple(mask.shape)}, the product {(M, N)}')
+    ldb = K + (-K) % 4
+    if M == 0 or N == 0 or not lib().dg_dense_supported(M, N, K, lda, ldb, a.data_ptr(), None, None):
+        return None
+    head, tail = split_operand(b, transposed, cache_key)
+    global dense_launches
+    dense_launches += (N + 255) // 256
     c = torch.empty((M, N), dtype=torch.float32, device=a.device)
     with torch.cuda.device(a.device):
         check(lib().dg_dense_nt_masked(a.data_ptr(), lda, head.data_ptr(), tail.data_ptr(), ldb, c.data_ptr(), N, M, N, K, int(relu),
@@ -522,7 +552,7 @@ def dense_tn(x, g):
     if scratch is None:
         scratch = _tn_scratch[x.device] = torch.empty(ctas * 256 * 256, dtype=torch.float32, device=x.device)
     global dense_launches
-    dense_launches += 2                 # the product and the reduction over the CTAs' partials
+    dense_launches += 2 * ((Km + 255) // 256) * ((Nn + 255) // 256)      # per 256 x 256 panel: the product and the reduction over the CTAs' partials
     d = torch.empty((Km, Nn), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
         check(lib().dg_dense_tn(x.data_ptr(), ldx, g.data_ptr(), ldg, d.data_ptr(), Nn, n, Km, Nn, scratch.data_ptr(), scratch.numel(),
@@ -530,8 +560,25 @@ def dense_tn(x, g):
     return d
 
 
-def dense_status():
-    """0, or non-zero if a dense-transform kernel gave up on one of its bounded waits since the process started."""
+def dense_status(reset=False):
+    """0, or non-zero if a dense-transform kernel gave up on one of its bounded waits since the last reset (its output is
+    then invalid).  Synchronises the current stream.  reset=True clears the word after reading it."""
     out = ctypes.c_int(-1)
     check(lib().dg_dense_status(ctypes.byref(out), _stream()))
+    if reset and out.value:
+        check(lib().dg_dense_status_reset(_stream()))
     return out.value
+
+
+def check_dense_status():
+    """Raises if a dense kernel gave up since the last check (and clears the word, so the next check starts fresh)."""
+    status = dense_status(reset=True)
+    if status:
+        raise RuntimeError('a dense-transform kernel gave up on a bounded wait: the activations or gradients of this step are invalid')
+
+
+def dense_wait_selftest():
+    """Runs the dense kernels' give-up path on purpose (dg_dense_wait_selftest); True if the bounded wait ran out as it must."""
+    out = ctypes.c_int(-1)
+    check(lib().dg_dense_wait_selftest(ctypes.byref(out), _stream()))
+    return out.value == 1

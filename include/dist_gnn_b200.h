@@ -230,9 +230,13 @@ int dg_comm_last_times(dg_comm* comm, dg_stage_times* host_out);
  * (Bt = W).  Three tcgen05 TF32 passes on head/tail splits with an fp32 accumulator in tensor memory give fp32-level
  * accuracy (about 5e-7 relative).  Bt is passed already split (dg_dense_split: head keeps sign, exponent and 10 mantissa
  * bits, tail = x - head); A is split inside the kernel.  Limits (dg_dense_supported returns 0 otherwise, and
- * dg_dense_nt DG_ERR_UNSUPPORTED): N <= 256, M < 2^31, lda and ldb multiples of 4 floats, A / Bt 16-byte aligned.
+ * dg_dense_nt DG_ERR_UNSUPPORTED): M < 2^31, lda and ldb multiples of 4 floats, A / Bt 16-byte aligned.  A result wider
+ * than 256 columns is computed in panels of 256 (A is streamed once per panel).
  * relu != 0 applies max(x, 0) on the way out.  dg_dense_status reads the device status word (synchronises `stream`):
- * non-zero if a kernel gave up on one of its bounded waits (its output is then invalid; nothing hangs). */
+ * non-zero if a kernel gave up on one of its bounded waits since the last dg_dense_status_reset (its output is then
+ * invalid; nothing hangs).  dg_dense_wait_selftest runs the give-up path on purpose, safely: one CTA allocates tensor
+ * memory, waits a few thousand polls on a barrier nothing arrives at, reports that the wait ran out (*host_gave_up = 1),
+ * frees its tensor memory and returns; the status word of the real kernels is not touched. */
 int dg_dense_split(const float* src, float* head, float* tail, int64_t count, void* stream);
 int dg_dense_supported(int64_t M, int32_t N, int32_t K, int64_t lda, int64_t ldb, const void* A, const void* Bt_head, const void* Bt_tail);
 int dg_dense_nt(const float* A, int64_t lda, const float* Bt_head, const float* Bt_tail, int64_t ldb, float* C, int64_t ldc,
@@ -246,15 +250,18 @@ int dg_dense_nt_masked(const float* A, int64_t lda, const float* Bt_head, const 
 /* Weight-gradient product D[Km x Nn] = X[n x Km]^T * G[n x Nn] (torch.mm at models/gcn.py:50), same arithmetic (three
  * TF32 passes, fp32 accumulator in tensor memory) with BOTH operands split inside the kernel.  The n rows are shared
  * out over at most max_ctas CTAs.  The tensor cores truncate when they add into their accumulator, an error that grows
- * with the number of rows, so every 256 rows (environment DG_DENSE_TN_FLUSH, in 16-row slabs) a CTA adds its
+ * with the number of rows, so every 256 rows a CTA adds its
  * accumulators, rounded to nearest, into its partial result in `scratch` and restarts them; a second kernel adds the
  * partials in CTA order, so the result is bit-reproducible and within about 6e-6 of the exact product for any n.
- * `scratch` is 16-byte aligned and holds ctas * roundup(Km, 128) * roundup(Nn, 16) floats (DG_ERR_SCRATCH otherwise).
- * Limits: Km, Nn <= 256, n < 2^31, ldx and ldg multiples of 4 floats, X / G 16-byte aligned. */
+ * `scratch` is 16-byte aligned and holds ctas * roundup(min(Km, 256), 128) * roundup(min(Nn, 256), 16) floats
+ * (DG_ERR_SCRATCH otherwise).  Wider results are computed as 256 x 256 panels of D, one after the other.
+ * Limits: n < 2^31, ldx and ldg multiples of 4 floats, X / G 16-byte aligned. */
 int dg_dense_tn_supported(int64_t n, int32_t Km, int32_t Nn, int64_t ldx, int64_t ldg, const void* X, const void* G);
 int dg_dense_tn(const float* X, int64_t ldx, const float* G, int64_t ldg, float* D, int64_t ldd, int64_t n, int32_t Km,
                 int32_t Nn, float* scratch, int64_t scratch_floats, int32_t max_ctas, void* stream);
 int dg_dense_status(int* host_status, void* stream);
+int dg_dense_status_reset(void* stream);
+int dg_dense_wait_selftest(int* host_gave_up, void* stream);
 
 /* ---- instrumentation (no counterpart in the reference, whose timer synchronises the device around every call,
  * light_dist_gnn/dist_utils/timer.py:16-24) ------------------------------------------------------------------------

@@ -32,7 +32,77 @@ def test_dense_split_is_exact_and_unsupported_shapes_fall_back():
     assert torch.equal(head + tail, w)
     assert torch.equal(head.view(torch.int32) & 8191, torch.zeros_like(head, dtype=torch.int32))
     assert spmm_cpp.dense_nt(torch.randn(100, 47, device='cuda'), torch.randn(16, 47, device='cuda')) is None     # 188-byte rows
-    assert spmm_cpp.dense_nt(torch.randn(100, 64, device='cuda'), torch.randn(300, 64, device='cuda')) is None     # N > 256
+
+
+@pytest.mark.parametrize('M,K,N', [(29121, 602, 256), (1000, 64, 300), (3000, 256, 602), (515, 604, 41)])
+def test_dense_nt_on_the_reddit_shaped_widths(M, K, N):
+    """Config 1's layer shapes (602 -> 256 -> 41 on 29,121-row blocks): an inner dimension of 602 read from rows padded to
+    604 floats, and results wider than one 256-column accumulator computed in panels."""
+    import spmm_cpp
+    g = torch.Generator(device='cuda').manual_seed(M + K + N)
+    wide = torch.randn(M, K + (-K) % 4, device='cuda', generator=g)
+    a = wide[:, :K]                                                # what the stage loop hands over for K = 602
+    w = torch.randn(K, N, device='cuda', generator=g)              # layer weight [in x out]
+    c = spmm_cpp.dense_nt(a, w, transposed=True, relu=True)
+    assert c is not None and c.shape == (M, N)
+    want = (a.double() @ w.double()).clamp(min=0)
+    assert_close(c.cpu().numpy(), want.cpu().numpy(), TOL, f'{M}x{K}x{N}')
+    # the split copy of a weight is kept until the weight changes in place
+    p = torch.nn.Parameter(w.clone())
+    first = spmm_cpp.dense_nt(a, p, transposed=True, cache_key=p)
+    assert torch.equal(first, spmm_cpp.dense_nt(a, p, transposed=True, cache_key=p))
+    with torch.no_grad():
+        p.mul_(2.0)
+    assert_close(spmm_cpp.dense_nt(a, p, transposed=True, cache_key=p).cpu().numpy(), (2 * (a.double() @ w.double())).cpu().numpy(), TOL, 'after an in-place update')
+    assert spmm_cpp.dense_status() == 0
+
+
+@pytest.mark.parametrize('n,Km,Nn', [(29121, 602, 256), (2000, 300, 300), (777, 256, 602), (4100, 604, 44)])
+def test_dense_tn_in_panels(n, Km, Nn):
+    """Weight gradients wider than two accumulators (config 1: X^T * AG with 602 input features) as 256 x 256 panels."""
+    import spmm_cpp
+    g = torch.Generator(device='cuda').manual_seed(n + Km + Nn)
+    x = torch.randn(n, Km + (-Km) % 4, device='cuda', generator=g)[:, :Km]
+    y = torch.randn(n, Nn + (-Nn) % 4, device='cuda', generator=g)[:, :Nn]
+    d = spmm_cpp.dense_tn(x, y)
+    assert d is not None and d.shape == (Km, Nn)
+    assert_close(d.cpu().numpy(), (x.double().t() @ y.double()).cpu().numpy(), TOL, f'{n}x{Km}x{Nn}')
+    assert torch.equal(d, spmm_cpp.dense_tn(x, y))
+    assert spmm_cpp.dense_status() == 0
+
+
+def test_dense_mm_pads_odd_row_strides_instead_of_leaving_the_tensor_cores():
+    """models.gcn.dense_mm on operands whose rows are not 16-byte multiples (602 input features, 41 classes, contiguous):
+    they are copied once into padded rows and still run on the hand-written kernels (the launch counter moves)."""
+    import spmm_cpp
+    from models.gcn import dense_mm
+    g = torch.Generator(device='cuda').manual_seed(602)
+    x = torch.randn(5000, 602, device='cuda', generator=g)
+    ag = torch.randn(5000, 41, device='cuda', generator=g)
+    w = torch.randn(602, 41, device='cuda', generator=g)
+    before = spmm_cpp.dense_launches
+    dw = dense_mm(x, ag, ta=True, constant_a=True)
+    out = dense_mm(x, w)
+    dx = dense_mm(ag, w, tb=True)
+    assert spmm_cpp.dense_launches > before + 3
+    assert_close(dw.cpu().numpy(), (x.double().t() @ ag.double()).cpu().numpy(), TOL, 'dW 602 x 41')
+    assert_close(out.cpu().numpy(), (x.double() @ w.double()).cpu().numpy(), TOL, 'X W')
+    assert_close(dx.cpu().numpy(), (ag.double() @ w.double().t()).cpu().numpy(), TOL, 'AG W^T, 602 wide')
+    assert spmm_cpp.dense_status() == 0
+
+
+def test_bounded_wait_gives_up_and_leaves_the_context_usable():
+    """The dense kernels bound every mbarrier wait.  dg_dense_wait_selftest runs that path on purpose - a wait on a barrier
+    nothing arrives at, with a short limit - and must report that the wait ran out, free its tensor memory and return;
+    the real kernels then run as before and their status word is untouched."""
+    import spmm_cpp
+    assert spmm_cpp.dense_wait_selftest() is True
+    a = torch.randn(300, 64, device='cuda')
+    w = torch.randn(64, 32, device='cuda')
+    c = spmm_cpp.dense_nt(a, w, transposed=True)                   # needs the tensor memory the self-test held
+    assert_close(c.cpu().numpy(), (a.double() @ w.double()).cpu().numpy(), TOL, 'product after the self-test')
+    assert spmm_cpp.dense_status() == 0
+    spmm_cpp.check_dense_status()
 
 
 @pytest.mark.parametrize('n,Km,Nn', [(16, 32, 16), (1000, 256, 256), (5000, 100, 256), (300, 128, 48), (70000, 256, 256),
@@ -106,5 +176,4 @@ def test_dense_kernels_take_column_slices_of_padded_buffers():
 
 def test_dense_tn_unsupported_shapes_fall_back():
     import spmm_cpp
-    assert spmm_cpp.dense_tn(torch.randn(100, 47, device='cuda'), torch.randn(100, 16, device='cuda')) is None
-    assert spmm_cpp.dense_tn(torch.randn(100, 64, device='cuda'), torch.randn(100, 300, device='cuda')) is None
+    assert spmm_cpp.dense_tn(torch.randn(100, 47, device='cuda'), torch.randn(100, 16, device='cuda')) is None      # 188-byte rows

@@ -231,3 +231,63 @@ def test_fused_relu_equals_separate_relu(golden, env1):
     assert (results[True][0] != 0).any()
     for a, b in zip(results[True][1], results[False][1]):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize('dense', ['host', 'cuda'])
+def test_plumbing_config_on_emulated_ranks_matches_the_reference_run(golden, dense, monkeypatch):
+    """BASELINE config 0 (10,000-node R-MAT, 128 -> 64 -> 10, Glorot weights, 2 ranks) with this package's loaders and
+    CUDA kernels, against what the unmodified reference produced for it on 2 gloo ranks (tests/golden/plumbing.npz):
+    every stage-loop result of epoch 0 (sampled rows, column sums, norms), dW after the all-reduce, 3 losses.  The two
+    ranks are emulated on one GPU: rank r adds plan(A[r, s]) @ X_s for s = 0, 1 in stage order.
+    dense='host': only the sparse products run on the GPU; dense='cuda': the dense transforms too (dg_dense_nt / _tn)."""
+    import spmm_cpp
+    from coo_graph import COO_Graph, Parted_COO_Graph, synthetic
+    from models.gcn import dense_mm
+    t = golden('plumbing')
+    cfg = synthetic.CONFIGS['plumbing']
+    full = COO_Graph.from_dict('plumbing', synthetic.make_dataset(seed=0, device='cuda', **cfg), device='cuda')
+    assert full.adj.values().numel() == int(t['full/adj_nnz'])
+    ranks = [Parted_COO_Graph.from_full(full, r, 2) for r in range(2)]
+    plans = [[spmm_cpp.plan_for(a) for a in g.adj_parts] for g in ranks]
+
+    def bcast(blocks):
+        xs = [torch.from_numpy(np.ascontiguousarray(b)).cuda() for b in blocks]
+        out = []
+        for r in range(2):
+            z = torch.empty_like(xs[r])
+            for s in range(2):
+                plans[r][s].spmm(xs[s], z, 1.0, 0.0 if s == 0 else 1.0)
+            out.append(z.cpu().numpy())
+        return out
+
+    if dense == 'cuda':
+        def mm(a, b):
+            if not a.flags['C_CONTIGUOUS'] and a.T.flags['C_CONTIGUOUS']:      # x^T @ ag: the weight-gradient kernel
+                return dense_mm(torch.from_numpy(a.T).cuda(), torch.from_numpy(np.ascontiguousarray(b)).cuda(), ta=True).cpu().numpy()
+            return dense_mm(torch.from_numpy(np.ascontiguousarray(a)).cuda(), torch.from_numpy(np.ascontiguousarray(b)).cuda()).cpu().numpy()
+        monkeypatch.setattr(ref_gcn, '_mm', mm)
+    dims = [cfg['feat_dim'], cfg['hidden'], cfg['num_classes']]
+    weights = [w.numpy() for w in synthetic.glorot_weights(dims, seed=0)]
+    model = ref_gcn.GcnOracle(bcast, weights, [[0, 1]])
+    feats = [g.features.cpu().numpy() for g in ranks]
+    labels = [g.local_labels.cpu().numpy() for g in ranks]
+    masks = [g.local_train_mask.cpu().numpy() for g in ranks]
+    rows = t['sample_rows']
+    for epoch in range(3):
+        losses, outputs, trace, btrace = model.epoch(feats, labels, masks)
+        for r in range(2):
+            want = t[f'r{r}/losses'][epoch]
+            assert abs(losses[r] - want) <= 2e-5 * max(1.0, abs(want)), (epoch, r, losses[r], want)
+        if epoch == 0:
+            for r in range(2):
+                got = [trace[0]['z'][r], trace[1]['z'][r], btrace[1]['ag'][r], btrace[0]['ag'][r]]
+                for i, g in enumerate(got):
+                    scale = float(t[f'r{r}/bcast_{i}/absmax'])
+                    assert np.abs(g[rows] - t[f'r{r}/bcast_{i}/rows']).max() <= TOL * scale, (r, i)
+                    assert np.abs(g.astype(np.float64).sum(0) - t[f'r{r}/bcast_{i}/colsum']).max() <= 1e-4 * scale * np.sqrt(g.shape[0])
+                    fro = float(t[f'r{r}/bcast_{i}/fro'])
+                    assert abs(np.sqrt((g.astype(np.float64) ** 2).sum()) - fro) <= TOL * fro
+                for l in range(2):
+                    assert_close(btrace[l]['dw'][r], t[f'r{r}/dw_{l}'], TOL, f'dW{l} rank {r}')
+    if dense == 'cuda':
+        assert spmm_cpp.dense_status() == 0

@@ -1,8 +1,9 @@
-"""The NCCL stage loop on real ranks: one process per GPU.  Skipped unless the box has at least 2 (or 4) GPUs.
+"""The stage loops on real ranks: one process per GPU.  Skipped unless the box has at least 2 (4, 8) GPUs.
 
 2 GPUs: the product's whole training path at P=2 against the values the reference itself produced on 2 gloo ranks.
-4 GPUs: the 1.5D schedule (P=4, c=2) against the oracle.  NVLS is switched off in the workers so that a failing
-worker cannot leave a multicast binding behind on the shared box.
+4 GPUs: the 1.5D schedule (P=4, c=2) against the oracle.
+8 GPUs: every 1D schedule at P=8, 1.5D at P=8 / c=2, and 3 epochs of training at P=8, against the oracle.
+NVLS is switched off in the workers so that a failing worker cannot leave a multicast binding behind on the shared box.
 """
 import os
 import sys
@@ -66,6 +67,8 @@ def _worker(rank, world, rep, port, out_dir, mode):
                 rec[f'zpg{i}'] = broadcast(g.adj_parts, x, f'w{width}').cpu().numpy()
                 env.stage_group, env.stage_order = 1, 'peer_compact'    # only the rows each reader's block touches travel (1D)
                 rec[f'zc{i}'] = broadcast(g.adj_parts, x, f'w{width}').cpu().numpy()
+                env.stage_group = (3, 2, 1)                             # the same with arrivals joined into fewer products
+                rec[f'zcg{i}'] = broadcast(g.adj_parts, x, f'w{width}').cpu().numpy()
                 env.stage_group, env.stage_order = 1, 'reference'
         torch.cuda.synchronize()
         np.savez(os.path.join(out_dir, f'rank{rank}.npz'), **rec)
@@ -110,7 +113,7 @@ def test_back_to_back_stage_loops_at_two_ranks(golden):
         want = ref_gcn.broadcast_1d([p['adj_parts'] for p in parts], [res[r][f'x{i}'] for r in range(2)])
         for r in range(2):
             assert_close(res[r][f'z{i}'], want[r], 1e-5, f'loop {i} rank {r}')
-            for key in ('zg', 'zl', 'zlg', 'zf', 'zp', 'zpg', 'zc'):
+            for key in ('zg', 'zl', 'zlg', 'zf', 'zp', 'zpg', 'zc', 'zcg'):
                 assert_close(res[r][f'{key}{i}'], want[r], 1e-5, f'{key} loop {i} rank {r}')
 
 
@@ -123,5 +126,50 @@ def test_15d_stage_loop_at_four_ranks(golden):
         want = ref_gcn.broadcast_15d([p['adj_parts'] for p in parts], [res[b * 2][f'x{i}'] for b in range(2)], 4, 2)
         for r in range(4):
             assert_close(res[r][f'z{i}'], want[r], 1e-5, f'loop {i} rank {r}')
-            for key in ('zg', 'zl', 'zlg', 'zf', 'zp', 'zpg', 'zc'):
+            for key in ('zg', 'zl', 'zlg', 'zf', 'zp', 'zpg', 'zc', 'zcg'):
                 assert_close(res[r][f'{key}{i}'], want[r], 1e-5, f'{key} loop {i} rank {r}')
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 8, reason='needs 8 GPUs')
+def test_every_1d_schedule_at_eight_ranks(golden):
+    from oracle import ref_gcn
+    res = _run(8, 1, 'loops', 29747)
+    parts = _oracle_blocks(golden, 8)
+    for i in range(4):
+        want = ref_gcn.broadcast_1d([p['adj_parts'] for p in parts], [res[r][f'x{i}'] for r in range(8)])
+        for r in range(8):
+            for key in ('z', 'zg', 'zl', 'zlg', 'zf', 'zp', 'zpg', 'zc', 'zcg'):
+                assert_close(res[r][f'{key}{i}'], want[r], 1e-5, f'{key} loop {i} rank {r}')
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 8, reason='needs 8 GPUs')
+def test_15d_stage_loop_at_eight_ranks(golden):
+    from oracle import ref_gcn
+    res = _run(8, 2, 'loops', 29749)
+    parts = _oracle_blocks(golden, 4)
+    for i in range(4):
+        want = ref_gcn.broadcast_15d([p['adj_parts'] for p in parts], [res[b * 2][f'x{i}'] for b in range(4)], 8, 2)
+        for r in range(8):
+            for key in ('z', 'zg', 'zl', 'zlg', 'zf', 'zp', 'zpg', 'zc', 'zcg'):
+                assert_close(res[r][f'{key}{i}'], want[r], 1e-5, f'{key} loop {i} rank {r}')
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 8, reason='needs 8 GPUs')
+def test_training_at_eight_ranks_matches_the_oracle(golden):
+    """3 epochs of dist_train.train at P=8 with the default schedule (reference initialiser) against the oracle's 8-rank
+    model: the first stage loop, each rank's losses, the weights after 3 Adam steps."""
+    from oracle import ref_gcn
+    res = _run(8, 1, 'train', 29751)
+    parts = _oracle_blocks(golden, 8)
+    torch.manual_seed(0)
+    w0 = [torch.rand(32, 16).numpy(), torch.rand(16, 16).numpy(), torch.rand(16, 7).numpy()]
+    oracle = ref_gcn.gcn_1d(parts, w0)
+    want_z = ref_gcn.broadcast_1d([p['adj_parts'] for p in parts], [p['features'] for p in parts])
+    for r in range(8):
+        assert_close(res[r]['z1'], want_z[r], 1e-5, f'first stage loop, rank {r}')
+    for epoch in range(3):
+        losses, *_ = oracle.epoch([p['features'] for p in parts], [p['local_labels'] for p in parts], [p['local_train_mask'] for p in parts])
+        for r in range(8):
+            assert abs(res[r]['losses'][epoch] - losses[r]) <= 2e-5 * max(1.0, abs(losses[r])), (r, epoch)
+    for l in range(3):
+        assert_close(res[0][f'w{l}'], oracle.weights[l], 1e-4, f'weights after 3 steps, layer {l}')

@@ -223,15 +223,36 @@ def test_compact_peer_loop_bookkeeping_simulated_on_the_host(P):
         assert np.allclose(z, want, rtol=1e-12, atol=1e-12)
 
 
-def test_reference_arm_sample_shapes_with_a_ragged_partition():
-    """bench.py --impl reference on a node count that the 16-way sample partition does not divide: the sampled row block
-    and the feature matrix agree in size and the CPU epoch runs."""
+def test_group_sizes_of_the_compact_loop():
+    from models.gcn import group_sizes
+    assert group_sizes(7, 1) == [1] * 7 and group_sizes(7, 3) == [3, 3, 1] and group_sizes(7, (4, 2, 1)) == [4, 2, 1]
+    assert group_sizes(7, (3, 1)) == [3, 1, 1, 1, 1] and group_sizes(0, 2) == [] and group_sizes(2, (5,)) == [2]
+
+
+def _tiny_bench_args():
     import argparse
+    return argparse.Namespace(seed=0, no_permute=False, config='ragged', rep=1, cpu_sample_divisor=4)
+
+
+TINY = dict(num_nodes=4012, directed_edges=32000, feat_dim=12, num_classes=5, split=(0.6, 0.2, 0.2), hidden=8, layers=3)
+
+
+def test_cpu_leg_port_runs_on_a_sample_and_scales_by_stored_entries():
+    """The fallback CPU leg of bench.py (the oracle's torch-CPU epoch) on a quarter-size sample of a small ragged config."""
     sys.path.insert(0, ROOT)
     import bench
-    cfg = dict(num_nodes=1003, directed_edges=8000, feat_dim=12, num_classes=5, split=(0.6, 0.2, 0.2), hidden=8, layers=2)
-    args = argparse.Namespace(seed=0, no_permute=False, config='ragged')
-    inp = bench.cpu_sample_inputs(cfg, args, torch.device('cpu'))
-    assert inp['adj'].size(1) == inp['x'].size(0) == 1003 and inp['adj'].size(0) == inp['n'] == 63
-    times, threads = bench.time_cpu_sample(inp, cfg, args, steps=1)
-    assert len(times) == 1 and times[0] > 0 and threads >= 1
+    small = bench.sample_config(TINY, 4)
+    assert small['num_nodes'] == 1003 and small['directed_edges'] == 8000
+    ms, info = bench.run_port_sample(TINY, _tiny_bench_args(), steps=1, warmup=0)
+    assert ms > 0 and info['kind'] == 'port' and 3.0 < info['scale'] < 5.0
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(ROOT, 'baseline', '_ref', 'light_dist_gnn')), reason='no copy of the reference in baseline/_ref')
+def test_cpu_leg_runs_the_unmodified_reference_over_gloo():
+    """bench.py's reference arm: the reference's own files (copied by __graft_entry__.build) train over gloo on part files
+    this package wrote, and report the reference timer's keys."""
+    sys.path.insert(0, ROOT)
+    import bench
+    ms, info = bench.run_reference_files(TINY, _tiny_bench_args(), steps=2, warmup=1)
+    assert ms > 0 and info['kind'] == 'reference' and info['cores'] >= 2
+    assert {'broadcast', 'spmm', 'mm', 'all_reduce', 'epoch'} <= set(info['reference_timer_s'])
