@@ -31,6 +31,26 @@ struct dg_comm {
     uint64_t peer_loops = 0;
     std::vector<cudaStream_t> peer_lanes;    // extra copy streams: a block is cut into pieces that travel side by side
     std::vector<cudaEvent_t> ev_lane;
+    // Set when a stage loop failed after it had started to enqueue: this rank's collectives or send-buffer parity may no
+    // longer match its peers', so every later loop on this communicator is refused with DG_ERR_STATE instead of hanging.
+    bool poisoned = false;
+};
+
+// Marks the communicator as poisoned unless the loop that created it ran to its end (call done()).
+struct IssueGuard {
+    dg_comm* c;
+    bool finished = false;
+    explicit IssueGuard(dg_comm* comm) : c(comm) {}
+    void done() { finished = true; }
+    ~IssueGuard() { if (!finished && c) c->poisoned = true; }
+};
+
+// ncclGroupStart / ncclGroupEnd as a scope: the group is closed on every path out of it, error returns included.
+struct NcclGroupScope {
+    bool open = false;
+    ncclResult_t begin() { ncclResult_t r = ncclGroupStart(); open = (r == ncclSuccess); return r; }
+    ncclResult_t end() { open = false; return ncclGroupEnd(); }
+    ~NcclGroupScope() { if (open) ncclGroupEnd(); }
 };
 
 inline int make_events(std::vector<cudaEvent_t>& v, size_t count, unsigned flags)

@@ -67,6 +67,7 @@ static inline int64_t dg_scratch_floats(const dg_plan* p, int32_t F)
     const int64_t a = (int64_t)p->n_chunks * F, b = 2 * (int64_t)p->n_tasks * F;
     return a > b ? a : b;
 }
+int dg_stream_selected();     // non-zero while dg_select_kernel(2) is in force
 int dg_spmm_stream_eligible(const dg_plan* plan, const float* B, int64_t ldb, const float* C, int64_t ldc, int32_t F);
 int dg_spmm_stream_launch(const dg_plan* plan, const float* val, const float* B, int64_t ldb, float* C, int64_t ldc,
                           int32_t F, float alpha, float beta, uint32_t flags, const float* row_scale, const float* bias,
@@ -80,5 +81,6 @@ int dg_spmm_launch(const dg_plan* plan, const float* val, const float* B, int64_
 int dg_spmm_launch_rows(const dg_plan* plan, const float* val, const float* B, int64_t ldb, float* C, int64_t ldc,
                         int32_t F, float alpha, float beta, uint32_t flags, const float* row_scale, const float* bias,
                         float* scratch, cudaStream_t stream);
+int dg_spmm_prepare(const dg_plan* plan, int32_t F, cudaStream_t stream);
 int dg_check_spmm_args(const dg_plan* plan, const float* val, const float* B, int64_t ldb, const float* C, int64_t ldc,
                        int32_t F, uint32_t flags, const float* row_scale, const float* bias);

@@ -211,12 +211,20 @@ int peer_loop(dg_comm* comm, dg_comm* row_comm, const PeerPacks& packs, int32_t 
     cudaStream_t compute = (cudaStream_t)compute_stream;
     const bool packed = packs.rows != nullptr || packs.stage_rows != nullptr;
     if (!comm) return DG_ERR_NULL;
+    if (comm->poisoned) return DG_ERR_STATE;
     if (packed) {
         if (packs.n_packs < 0 || (packs.n_packs > 0 && (!packs.rows || !packs.counts || !packs.offsets))) return DG_ERR_NULL;
         if (n_stages > 0 && (!packs.stage_offsets || !packs.stage_rows)) return DG_ERR_NULL;
         for (int q = 0; q < packs.n_packs; ++q) {
             if (packs.counts[q] < 0 || packs.offsets[q] < 0 || (packs.counts[q] > 0 && !packs.rows[q])) return DG_ERR_DIMS;
             if ((packs.offsets[q] + packs.counts[q]) * (int64_t)F > comm->peer_floats) return DG_ERR_SCRATCH;
+        }
+        // what this rank reads from its peers: every rank allocates send buffers of the same size (peer_floats), so a range
+        // that fits this rank's buffers fits the root's; a layout that disagrees between ranks is refused here, on the
+        // host, instead of sending a copy engine past the end of a peer's mapping
+        for (int s = 0; s < n_stages; ++s) {
+            if (packs.stage_rows[s] < 0 || packs.stage_offsets[s] < 0) return DG_ERR_DIMS;
+            if ((packs.stage_offsets[s] + packs.stage_rows[s]) * (int64_t)F > comm->peer_floats) return DG_ERR_SCRATCH;
         }
     }
     if (n_stages < 0 || n_products < 0 || n < 0 || F < 0) return DG_ERR_DIMS;
@@ -242,11 +250,15 @@ int peer_loop(dg_comm* comm, dg_comm* row_comm, const PeerPacks& packs, int32_t 
     if (timed) {
         if ((rc = make_events(comm->t_comm, 2 * (size_t)n_products, cudaEventDefault))) return rc;
         if ((rc = make_events(comm->t_spmm, 2 * (size_t)n_products, cudaEventDefault))) return rc;
-        DG_CUDA(cudaEventRecord(comm->t_begin, compute));
     }
+    for (int p = 0; p < n_products; ++p)                          // scratch growth (it allocates) happens before anything is enqueued
+        if ((rc = dg_spmm_prepare(plans[p], F, compute))) return rc;
+    // From here on a failure leaves this rank out of step with its peers (a missed meeting point, a send-buffer parity that
+    // differs): the guard then marks the communicator and later loops are refused.
+    IssueGuard issue(comm);
+    if (timed) DG_CUDA(cudaEventRecord(comm->t_begin, compute));
     if (n_products == 0 && count) DG_CUDA(cudaMemsetAsync(z, 0, count * sizeof(float), compute));
     const int b = (int)(comm->peer_loops & 1);
-    comm->peer_loops++;
     // this rank's block goes where its peers can read it; everything queued so far on the compute stream comes first
     if (packed) {
         for (int q = 0; q < packs.n_packs && count; ++q) {
@@ -309,6 +321,8 @@ int peer_loop(dg_comm* comm, dg_comm* row_comm, const PeerPacks& packs, int32_t 
         DG_CUDA(cudaEventRecord(comm->t_end, compute));
         comm->timed_stages = n_products;
     }
+    comm->peer_loops++;                                           // the loop is fully issued: the next one uses the other send buffer
+    issue.done();
     return DG_OK;
 }
 

@@ -79,6 +79,7 @@ int stage_loop(dg_comm* comm, int32_t n_stages, const int32_t* roots, int32_t gr
         }
         return DG_OK;
     }
+    if (comm->poisoned) return DG_ERR_STATE;
     DeviceGuard guard(comm->device);
     if ((rc = make_events(comm->ev_arrived, (size_t)nbuf, cudaEventDisableTiming))) return rc;
     if ((rc = make_events(comm->ev_free, (size_t)nbuf, cudaEventDisableTiming))) return rc;
@@ -86,8 +87,11 @@ int stage_loop(dg_comm* comm, int32_t n_stages, const int32_t* roots, int32_t gr
     if (timed) {
         if ((rc = make_events(comm->t_comm, 2 * (size_t)n_groups, cudaEventDefault))) return rc;
         if ((rc = make_events(comm->t_spmm, 2 * (size_t)n_groups, cudaEventDefault))) return rc;
-        DG_CUDA(cudaEventRecord(comm->t_begin, compute));
     }
+    for (int g = 0; g < n_groups; ++g)                  // scratch growth (it allocates) happens before anything is enqueued
+        if ((rc = dg_spmm_prepare(plans[g], F, compute))) return rc;
+    IssueGuard issue(comm);
+    if (timed) DG_CUDA(cudaEventRecord(comm->t_begin, compute));
     // Everything already queued on the compute stream (the producer of x_local, earlier readers of recv[]) comes first.
     DG_CUDA(cudaEventRecord(comm->ev_input, compute));
     DG_CUDA(cudaStreamWaitEvent(comm->side, comm->ev_input, 0));
@@ -102,10 +106,11 @@ int stage_loop(dg_comm* comm, int32_t n_stages, const int32_t* roots, int32_t gr
         if (!in_place && g >= nbuf) DG_CUDA(cudaStreamWaitEvent(comm->side, comm->ev_free[b], 0));
         if (timed) DG_CUDA(cudaEventRecord(comm->t_comm[2 * g], comm->side));
         if (count) {
-            if (in_group > 1) DG_NCCL(ncclGroupStart());
+            NcclGroupScope scope;
+            if (in_group > 1) DG_NCCL(scope.begin());
             for (int j = 0; j < in_group; ++j)
                 DG_NCCL(ncclBroadcast(x_local, landing + (size_t)j * count, count, ncclFloat, roots[s0 + j], comm->comm, comm->side));
-            if (in_group > 1) DG_NCCL(ncclGroupEnd());
+            if (in_group > 1) DG_NCCL(scope.end());
         }
         if (timed) DG_CUDA(cudaEventRecord(comm->t_comm[2 * g + 1], comm->side));
         DG_CUDA(cudaEventRecord(comm->ev_arrived[b], comm->side));
@@ -120,6 +125,7 @@ int stage_loop(dg_comm* comm, int32_t n_stages, const int32_t* roots, int32_t gr
         DG_CUDA(cudaEventRecord(comm->t_end, compute));
         comm->timed_stages = n_groups;
     }
+    issue.done();
     return DG_OK;
 }
 
@@ -245,15 +251,20 @@ extern "C" int dg_bcast_spmm_ordered(dg_comm* comm, dg_comm* row_comm, int32_t n
         if (plans[p]->m != n || last_stage[p] >= n_stages || (last_stage[p] >= 0 && last_stage[p] < prev)) return DG_ERR_DIMS;
         if (last_stage[p] > prev) prev = last_stage[p];
     }
+    if (comm->poisoned) return DG_ERR_STATE;
     int rc;
     DeviceGuard guard(comm->device);
     if ((rc = make_events(comm->ev_arrived, (size_t)n_products, cudaEventDisableTiming))) return rc;
+    if ((rc = make_events(comm->ev_free, 1, cudaEventDisableTiming))) return rc;
     comm->timed_stages = 0;
     if (timed) {
         if ((rc = make_events(comm->t_comm, 2 * (size_t)n_products, cudaEventDefault))) return rc;
         if ((rc = make_events(comm->t_spmm, 2 * (size_t)n_products, cudaEventDefault))) return rc;
-        DG_CUDA(cudaEventRecord(comm->t_begin, compute));
     }
+    for (int p = 0; p < n_products; ++p)                // scratch growth (it allocates) happens before anything is enqueued
+        if ((rc = dg_spmm_prepare(plans[p], F, compute))) return rc;
+    IssueGuard issue(comm);
+    if (timed) DG_CUDA(cudaEventRecord(comm->t_begin, compute));
     if (n_products == 0 && count) DG_CUDA(cudaMemsetAsync(z, 0, count * sizeof(float), compute));
     // the producer of x_local and every earlier reader of the landing area are already queued on the compute stream
     DG_CUDA(cudaEventRecord(comm->ev_input, compute));
@@ -264,12 +275,13 @@ extern "C" int dg_bcast_spmm_ordered(dg_comm* comm, dg_comm* row_comm, int32_t n
         while (issued < until) {
             const int end = issued + bcast_group < n_stages ? issued + bcast_group : n_stages;
             if (count && comm->nranks > 1) {
-                if (end - issued > 1) DG_NCCL(ncclGroupStart());
+                NcclGroupScope scope;
+                if (end - issued > 1) DG_NCCL(scope.begin());
                 for (int s = issued; s < end; ++s) {
                     float* dst = roots[s] == comm->rank && !landing[s] ? const_cast<float*>(x_local) : landing[s];
                     DG_NCCL(ncclBroadcast(x_local, dst, count, ncclFloat, roots[s], comm->comm, comm->side));
                 }
-                if (end - issued > 1) DG_NCCL(ncclGroupEnd());
+                if (end - issued > 1) DG_NCCL(scope.end());
             }
             issued = end;
         }
@@ -291,7 +303,6 @@ extern "C" int dg_bcast_spmm_ordered(dg_comm* comm, dg_comm* row_comm, int32_t n
     if (issued < n_stages) {    // broadcasts no product of this rank reads (it only roots them): still its part of the collective
         if ((rc = issue_until(n_stages))) return rc;
         // later work on the compute stream may overwrite x_local: it has to wait until the send has read it
-        if ((rc = make_events(comm->ev_free, 1, cudaEventDisableTiming))) return rc;
         DG_CUDA(cudaEventRecord(comm->ev_free[0], comm->side));
         DG_CUDA(cudaStreamWaitEvent(compute, comm->ev_free[0], 0));
     }
@@ -303,6 +314,7 @@ extern "C" int dg_bcast_spmm_ordered(dg_comm* comm, dg_comm* row_comm, int32_t n
         DG_CUDA(cudaEventRecord(comm->t_end, compute));
         comm->timed_stages = n_products;
     }
+    issue.done();
     return DG_OK;
 }
 
@@ -327,6 +339,7 @@ extern "C" int dg_allgather_spmm(dg_comm* comm, const dg_plan* plan, const float
     if (total != F) return DG_ERR_DIMS;
     if ((int64_t)n * F == 0) return DG_OK;
     if (!x_local || !z || !area || !area[0] || !area[1] || (n_chunks > 1 && (!pack || !pack[0] || !pack[1]))) return DG_ERR_NULL;
+    if (comm->poisoned) return DG_ERR_STATE;
     int rc;
     DeviceGuard guard(comm->device);
     if ((rc = make_events(comm->ev_arrived, 2, cudaEventDisableTiming))) return rc;
@@ -336,8 +349,12 @@ extern "C" int dg_allgather_spmm(dg_comm* comm, const dg_plan* plan, const float
     if (timed) {
         if ((rc = make_events(comm->t_comm, 2 * (size_t)n_chunks, cudaEventDefault))) return rc;
         if ((rc = make_events(comm->t_spmm, 2 * (size_t)n_chunks, cudaEventDefault))) return rc;
-        DG_CUDA(cudaEventRecord(comm->t_begin, compute));
     }
+    int widest = 0;
+    for (int c = 0; c < n_chunks; ++c) widest = chunk_widths[c] > widest ? chunk_widths[c] : widest;
+    if ((rc = dg_spmm_prepare(plan, widest, compute))) return rc;     // scratch growth before anything is enqueued
+    IssueGuard issue(comm);
+    if (timed) DG_CUDA(cudaEventRecord(comm->t_begin, compute));
     auto stage_in = [&](int c, int c0) -> int {      // pack chunk c on the compute stream, gather it on the side stream
         const int b = c & 1, w = chunk_widths[c];
         const float* send = x_local;
@@ -372,6 +389,7 @@ extern "C" int dg_allgather_spmm(dg_comm* comm, const dg_plan* plan, const float
         DG_CUDA(cudaEventRecord(comm->t_end, compute));
         comm->timed_stages = n_chunks;
     }
+    issue.done();
     return DG_OK;
 }
 

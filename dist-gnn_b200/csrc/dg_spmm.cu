@@ -524,6 +524,25 @@ extern "C" int dg_profile_end(dg_profile* out)
     return DG_OK;
 }
 
+// Grows the plan's scratch to what a product of width F may need (either kernel family); allocates and synchronises
+// `stream` only when it has to grow.  The stage loops call it for every plan before they enqueue anything, so that an
+// allocation failure cannot leave a loop half issued.
+int dg_spmm_prepare(const dg_plan* plan, int32_t F, cudaStream_t stream)
+{
+    if (!plan) return DG_ERR_NULL;
+    dg_plan* p = const_cast<dg_plan*>(plan);
+    const int64_t need = dg_stream_selected() ? dg_scratch_floats(plan, F) : (int64_t)plan->n_chunks * F;
+    if (need > p->scratch_floats) {
+        DG_CUDA(cudaStreamSynchronize(stream));
+        cudaFree(p->scratch);
+        p->scratch = nullptr;
+        p->scratch_floats = 0;
+        DG_CUDA(cudaMalloc((void**)&p->scratch, (size_t)need * sizeof(float)));
+        p->scratch_floats = need;
+    }
+    return DG_OK;
+}
+
 extern "C" int dg_spmm_csr(const dg_plan* plan, const float* val, const float* B, int64_t ldb, float* C, int64_t ldc,
                            int32_t F, float alpha, float beta, uint32_t flags, const float* row_scale,
                            const float* bias, void* stream)

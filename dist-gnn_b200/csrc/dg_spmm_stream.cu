@@ -265,6 +265,8 @@ extern "C" int dg_select_kernel(int family)
     return DG_OK;
 }
 
+int dg_stream_selected() { return tuning().choice == 2; }
+
 int dg_spmm_stream_eligible(const dg_plan* plan, const float* B, int64_t ldb, const float* C, int64_t ldc, int32_t F)
 {
     if (tuning().choice != 2) return 0;      // opt-in: on B200 the row kernels are at least as fast (see the header comment)

@@ -34,8 +34,10 @@ def local_loss(g, outputs, loss_func):
     return (outputs * 0).sum()
 
 
-def train(g, env, total_epoch, hidden_dim=256, num_layers=3, weights=None, log_every=10):
-    model = GCN(g, env, hidden_dim=hidden_dim, num_layers=num_layers, weights=weights)
+def train(g, env, total_epoch, hidden_dim=256, num_layers=3, weights=None, log_every=10, **model_options):
+    """The reference's epoch loop (dist_train.py:26-55).  model_options go to GCN (cache_input_product,
+    input_gradient_shortcut); the defaults recompute everything every epoch, as the reference does."""
+    model = GCN(g, env, hidden_dim=hidden_dim, num_layers=num_layers, weights=weights, **model_options)
     optimizer = torch.optim.Adam(model.parameters(), lr=0.01)
     loss_func = nn.CrossEntropyLoss() if g.labels.dim() == 1 else nn.BCEWithLogitsLoss(reduction='mean')
     losses = []

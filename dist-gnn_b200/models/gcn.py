@@ -227,6 +227,10 @@ def compact_exchange(env, adj_parts, stages):
     gathered = [None] * size
     dist.all_gather_object(gathered, wanted, group=env.world_group)   # gathered[q][s]: rows of block s that reader q needs
     lay = schedule.compact_layout(gathered, me, [stages[i].root_in_group for i in kept])
+    for q, _ in lay['packs']:                                         # the rows a reader asks for must exist in this rank's block
+        ids = gathered[q][me]
+        if len(ids) and (int(ids.min()) < 0 or int(ids.max()) >= n):
+            raise RuntimeError(f'rank {q} asked rank {me} for rows outside its block of {n} rows')
     packs = [(torch.from_numpy(gathered[q][me]).to(env.device), offset) for q, offset in lay['packs']]
     plans, plan_slices, plan_last = [], [], []
     first = 0
@@ -314,21 +318,30 @@ def group_plans(adj_parts, parts, group):
 
 
 class DistGCNLayer(torch.autograd.Function):
-    """forward(features, weight, adj_parts, tag) as in the reference (gcn.py:35-53).  Two optional flags let GCN fuse the
+    """forward(features, weight, adj_parts, tag) as in the reference (gcn.py:35-53).  Optional flags let GCN fuse the
     ReLU between two layers into the dense kernels instead of running it (and its backward) as separate passes:
 
     relu            the layer returns max(out, 0).  Its backward then expects a grad_output that is ALREADY zero where
                     the returned activation is zero - which is what the next layer delivers when it is called with
     input_is_relu   this layer's input is such an activation: the gradient it returns for the input is zeroed where
                     the input is <= 0 (the ReLU's backward, applied in the epilogue of AG * W^T).
-    Used as a pair they compute exactly  relu(layer(x))  and its gradient; one without the other does not."""
+    Used as a pair they compute exactly  relu(layer(x))  and its gradient; one without the other does not.
+
+    product         a precomputed  sum_s A[rank, s] X_s  for these very features (GCN's cache of the first layer's
+                    product, whose operand never changes): the stage loop of the forward pass is skipped.
+    shortcut        only with `product`, and only when the input needs no gradient: the weight gradient is taken as
+                    product^T * grad_output instead of X^T * (A * grad_output), which skips the backward stage loop too.
+                    Summed over the ranks the two are the same matrix when A is symmetric - the assumption the reference
+                    already makes by multiplying with the un-transposed row block in backward (gcn.py:47) - but each
+                    rank's term, and the rounding, differ."""
 
     @staticmethod
-    def forward(ctx, features, weight, adj_parts, tag, relu=False, input_is_relu=False):
-        ctx.save_for_backward(features, weight)
+    def forward(ctx, features, weight, adj_parts, tag, relu=False, input_is_relu=False, product=None, shortcut=False):
         ctx.adj_parts, ctx.tag, ctx.input_is_relu = adj_parts, tag, input_is_relu
         ctx.weight_key = weight                      # the caller's tensor object: key of the split-weight cache
-        z_local = broadcast(adj_parts, features, 'Forward' + tag)
+        ctx.shortcut = bool(shortcut and product is not None)
+        z_local = product if product is not None else broadcast(adj_parts, features, 'Forward' + tag)
+        ctx.save_for_backward(z_local if ctx.shortcut else features, weight)
         with DistEnv.env.timer.timing_cuda('mm'):
             z_local = dense_mm(z_local, weight, relu=relu, weight_key=weight)
         return z_local
@@ -336,6 +349,14 @@ class DistGCNLayer(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         features, weight = ctx.saved_tensors
+        if ctx.shortcut and not ctx.needs_input_grad[0]:
+            with DistEnv.env.timer.timing_cuda('mm'):
+                grad_weight = dense_mm(features, grad_output, ta=True, constant_a=True)      # `features` holds the saved product here
+            with DistEnv.env.timer.timing_cuda('all_reduce'):
+                DistEnv.env.all_reduce_sum(grad_weight)
+            return None, grad_weight, None, None, None, None, None, None
+        if ctx.shortcut:
+            raise RuntimeError('the gradient shortcut needs an input that requires no gradient')
         ag = broadcast(ctx.adj_parts, grad_output, 'Backward' + ctx.tag)
         with DistEnv.env.timer.timing_cuda('mm'):
             grad_features = None
@@ -344,18 +365,30 @@ class DistGCNLayer(torch.autograd.Function):
             grad_weight = dense_mm(features, ag, ta=True, constant_a=not ctx.needs_input_grad[0])
         with DistEnv.env.timer.timing_cuda('all_reduce'):
             DistEnv.env.all_reduce_sum(grad_weight)
-        return grad_features, grad_weight, None, None, None, None
+        return grad_features, grad_weight, None, None, None, None, None, None
 
 
 class GCN(nn.Module):
     """num_layers DistGCNLayers with ReLU between them, no bias (gcn.py:56-72).  Weights are drawn as the reference
     draws them - torch.rand on the host after manual_seed(0), layer by layer - unless `weights` injects them.
     The ReLUs run inside the dense kernels (FUSE_RELU); with DIST_GNN_FUSE_RELU=0 they are F.relu calls as in the
-    reference."""
+    reference.
 
-    def __init__(self, g, env, hidden_dim=16, num_layers=3, weights=None):
+    cache_input_product     keep the first layer's  sum_s A[rank, s] X_s  between epochs: its operand is the input
+                            features, which never change (gcn.py:69 recomputes it every epoch).  Exact: the losses are
+                            bit-identical to the uncached run.  The cache is dropped when a different features tensor
+                            is passed in or the tensor is modified in place.
+    input_gradient_shortcut with the cache, also take the first layer's weight gradient from the cached product (see
+                            DistGCNLayer `shortcut`): no stage loop at all for layer 1.  Equal to the reference's
+                            gradient for a symmetric adjacency up to rounding, not bit for bit.
+    Both are off by default: the like-for-like epoch recomputes everything, as the reference does."""
+
+    def __init__(self, g, env, hidden_dim=16, num_layers=3, weights=None, cache_input_product=False, input_gradient_shortcut=False):
         super().__init__()
         self.g, self.env, self.num_layers = g, env, num_layers
+        self.cache_input_product = bool(cache_input_product or input_gradient_shortcut)
+        self.input_gradient_shortcut = bool(input_gradient_shortcut)
+        self._product = None        # (features tensor, its version, the cached product)
         in_dim, out_dim = g.features.size(1), g.num_classes
         dims = [in_dim] + [hidden_dim] * (num_layers - 1) + [out_dim]
         torch.manual_seed(0)
@@ -367,14 +400,29 @@ class GCN(nn.Module):
     def weights(self):
         return [getattr(self, f'weight{l + 1}') for l in range(self.num_layers)]
 
+    def input_product(self, features):
+        """The cached first-layer product for `features`, computed on first use (None when caching is off or the features
+        take part in autograd)."""
+        if not self.cache_input_product or features.requires_grad:
+            return None
+        hit = self._product
+        if hit is None or hit[0] is not features or hit[1] != features._version:
+            with torch.no_grad():
+                z = broadcast(self.g.adj_parts, features, 'ForwardL1')
+                z = z.clone() if z.data_ptr() != z.untyped_storage().data_ptr() or not z.is_contiguous() else z   # own its memory
+            self._product = hit = (features, features._version, z)
+        return hit[2]
+
     def forward(self, features):
         h = features
         last = self.num_layers - 1
         for l, w in enumerate(self.weights()):
+            product = self.input_product(h) if l == 0 else None
+            shortcut = self.input_gradient_shortcut and product is not None
             if FUSE_RELU:
-                h = DistGCNLayer.apply(h, w, self.g.adj_parts, f'L{l + 1}', l < last, l > 0)
+                h = DistGCNLayer.apply(h, w, self.g.adj_parts, f'L{l + 1}', l < last, l > 0, product, shortcut)
             else:
-                h = DistGCNLayer.apply(h, w, self.g.adj_parts, f'L{l + 1}')
+                h = DistGCNLayer.apply(h, w, self.g.adj_parts, f'L{l + 1}', False, False, product, shortcut)
                 if l < last:
                     h = F.relu(h)
         return h

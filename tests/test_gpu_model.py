@@ -291,3 +291,45 @@ def test_plumbing_config_on_emulated_ranks_matches_the_reference_run(golden, den
                     assert_close(btrace[l]['dw'][r], t[f'r{r}/dw_{l}'], TOL, f'dW{l} rank {r}')
     if dense == 'cuda':
         assert spmm_cpp.dense_status() == 0
+
+
+def test_cached_input_product_gives_bit_identical_training(golden, env1):
+    """GCN(cache_input_product=True) keeps the first layer's A X between epochs: same losses and weights bit for bit;
+    the cache follows the features tensor (a new tensor or an in-place change recomputes it)."""
+    import dist_train
+    from coo_graph import COO_Graph, Parted_COO_Graph
+    from models.gcn import broadcast
+    z = golden('graph_small')
+    g = Parted_COO_Graph.from_full(COO_Graph.from_dict('gsmall', _fixture_dataset(z), device='cuda'), 0, 1)
+    plain_model, plain = dist_train.train(g, env1, total_epoch=4, hidden_dim=16, num_layers=3)
+    cached_model, cached = dist_train.train(g, env1, total_epoch=4, hidden_dim=16, num_layers=3, cache_input_product=True)
+    assert plain == cached
+    for a, b in zip(plain_model.weights(), cached_model.weights()):
+        assert torch.equal(a.detach(), b.detach())
+    first = cached_model.input_product(g.features)
+    assert first is cached_model.input_product(g.features)                    # a hit
+    assert torch.equal(first, broadcast(g.adj_parts, g.features, 'check'))
+    other = (g.features * 2).contiguous()
+    assert torch.equal(cached_model.input_product(other), broadcast(g.adj_parts, other, 'check'))      # another tensor
+    other.mul_(0.5)
+    assert torch.equal(cached_model.input_product(other), first)              # changed in place: recomputed
+    assert plain_model.input_product(g.features) is None                      # caching is off by default
+
+
+def test_input_gradient_shortcut_matches_within_rounding(golden, env1):
+    """GCN(input_gradient_shortcut=True): dW1 = (A X)^T G instead of X^T (A G).  Equal for the symmetric normalised
+    adjacency up to rounding: losses within 2e-5, weights after 4 steps within 1e-4, and no stage loop runs for layer 1."""
+    import dist_train
+    import spmm_cpp
+    from coo_graph import COO_Graph, Parted_COO_Graph
+    z = golden('graph_small')
+    g = Parted_COO_Graph.from_full(COO_Graph.from_dict('gsmall', _fixture_dataset(z), device='cuda'), 0, 1)
+    plain_model, plain = dist_train.train(g, env1, total_epoch=4, hidden_dim=16, num_layers=3)
+    spmm_cpp.profile_begin()
+    short_model, short = dist_train.train(g, env1, total_epoch=4, hidden_dim=16, num_layers=3, input_gradient_shortcut=True)
+    prof = spmm_cpp.profile_end()
+    assert prof['products'] == 1 + 4 * 4            # the cached product once, then 2 forward + 2 backward loops per epoch
+    for a, b in zip(plain, short):
+        assert abs(a - b) <= 2e-5 * max(1.0, abs(a))
+    for a, b in zip(plain_model.weights(), short_model.weights()):
+        assert_close(b.detach().cpu().numpy(), a.detach().cpu().numpy(), 1e-4, 'weights with the gradient shortcut')
