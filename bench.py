@@ -261,7 +261,8 @@ def run_ours(args):
         comm_info = measure_stage_loops(env, g, sorted(set(dims)), spmm_cpp)
 
     # ---- parity of the distributed product with a direct fp64 evaluation of sampled rows (outside every timed region) ----
-    parity = parity_check(env, g, sorted({dims[1], dims[-1]}))
+    from dist_utils.selfcheck import sampled_rows_check
+    parity = sampled_rows_check(env, g.adj, g.adj_parts, sorted({dims[1], dims[-1]}))
 
     # per-rank product time: report the slowest rank's (it sets the epoch time)
     gathered = env.all_gather_object(prof) if world > 1 else [prof]
@@ -308,51 +309,6 @@ def run_ours(args):
     env.shutdown()
     if not parity['ok']:
         raise SystemExit(f"parity check failed: {parity}")
-
-
-PARITY_TOL = 1e-5
-PARITY_ROWS = 384
-
-
-def parity_check(env, g, widths):
-    """The distributed product of the active schedule against a direct evaluation that shares nothing with it: every rank
-    draws a seeded operand block, runs  z = sum_s A[rank, s] X_s  through the model's own stage loop (models.gcn.broadcast),
-    gathers all operand blocks with torch.distributed, and recomputes PARITY_ROWS sampled rows of its block of A (the
-    longest row among them) in float64 with plain index arithmetic on the row block's COO entries.  Pins what
-    light_dist_gnn/models/gcn.py:16-30 computes.  Returns the worst relative errors over ranks and widths."""
-    from models.gcn import broadcast
-    dev, n = env.device, g.local_num_nodes
-    idx, val = g.adj.indices(), g.adj.values()
-    row = idx[0].contiguous()
-    gen = torch.Generator(device='cpu').manual_seed(977 + env.rank)
-    counts = torch.bincount(row, minlength=n)
-    sample = torch.cat((torch.randperm(n, generator=gen)[:PARITY_ROWS - 1].to(dev), counts.argmax().view(1))).unique()
-    lo = torch.searchsorted(row, sample)
-    hi = torch.searchsorted(row, sample, right=True)
-    lengths = hi - lo
-    slot = torch.repeat_interleave(torch.arange(sample.numel(), device=dev), lengths)        # entry -> sampled row
-    offsets = torch.arange(int(lengths.sum()), device=dev) - torch.repeat_interleave(lengths.cumsum(0) - lengths, lengths)
-    entries = torch.repeat_interleave(lo, lengths) + offsets
-    cols, vals = idx[1][entries], val[entries].double()
-    worst = {'max_rel': 0.0, 'fro_rel': 0.0}
-    for width in widths:
-        x = torch.randn(n, width, generator=torch.Generator(device='cpu').manual_seed(31 * width + env.rank // env.rep)).to(dev)
-        z = broadcast(g.adj_parts, x, f'parity{width}')
-        x_all = env.all_gather_then_cat(x) if env.world_size > 1 else x
-        want = torch.zeros(sample.numel(), width, dtype=torch.float64, device=dev)
-        for c0 in range(0, entries.numel(), 1 << 20):                                        # bounded temporaries
-            sl = slice(c0, c0 + (1 << 20))
-            want.index_add_(0, slot[sl], vals[sl, None] * x_all[cols[sl]].double())
-        got = z[sample].double()
-        worst['max_rel'] = max(worst['max_rel'], float((got - want).abs().max() / want.abs().max().clamp(min=1e-30)))
-        worst['fro_rel'] = max(worst['fro_rel'], float((got - want).norm() / want.norm().clamp(min=1e-30)))
-    every = env.all_gather_object(worst) if env.world_size > 1 else [worst]
-    out = {'max_rel': max(w['max_rel'] for w in every), 'fro_rel': max(w['fro_rel'] for w in every),
-           'rows': int(sample.numel()) * env.world_size, 'widths': list(widths), 'tolerance': PARITY_TOL,
-           'against': 'float64 evaluation of sampled rows of every rank\'s row block on operands gathered with torch.distributed',
-           'schedule': env.stage_order, 'stage_group': env.stage_group}
-    out['ok'] = bool(out['max_rel'] <= PARITY_TOL and out['fro_rel'] <= PARITY_TOL)
-    return out
 
 
 def measure_stage_loops(env, g, widths, spmm_cpp):
