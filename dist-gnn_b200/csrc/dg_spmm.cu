@@ -328,7 +328,7 @@ __global__ void __launch_bounds__(256, DG_V4_MIN_BLOCKS) k_spmm_v4(const SpmmArg
         if (chunk_id >= a.n_chunks) return;
         const dg_chunk ch = a.chunks[chunk_id];
         gather_v4<U>(bl, ld4, a.col + ch.e0 + lane, a.val + ch.e0 + lane, (int)(ch.e1 - ch.e0), on, acc);
-        if (on) reinterpret_cast<float4*>(a.scratch + (size_t)ch.slot * (size_t)a.F)[vec0] = acc;
+        if (on) __stcs(reinterpret_cast<float4*>(a.scratch + (size_t)ch.slot * (size_t)a.F) + vec0, acc);
         return;
     }
     const int32_t row0 = ((int)blockIdx.x - chunk_ctas) * a.rows_per_cta;     // m < 2^31
@@ -345,14 +345,14 @@ __global__ void __launch_bounds__(256, DG_V4_MIN_BLOCKS) k_spmm_v4(const SpmmArg
             if (on) {
                 float4* cp = reinterpret_cast<float4*>(a.C + (size_t)i * (size_t)a.ldc) + vec0;
                 float4 old = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (a.beta != 0.f) old = *cp;
+                if (a.beta != 0.f) old = __ldcs(cp);            // the result streams through: it must not displace rows of B in L2
                 if constexpr (PLAIN) {
-                    *cp = make_float4(fmaf(a.beta, old.x, acc.x), fmaf(a.beta, old.y, acc.y), fmaf(a.beta, old.z, acc.z),
-                                      fmaf(a.beta, old.w, acc.w));
+                    __stcs(cp, make_float4(fmaf(a.beta, old.x, acc.x), fmaf(a.beta, old.y, acc.y), fmaf(a.beta, old.z, acc.z),
+                                           fmaf(a.beta, old.w, acc.w)));
                 } else {
                     const int c = vec0 * 4;
-                    *cp = make_float4(finish(a, acc.x, old.x, i, c), finish(a, acc.y, old.y, i, c + 1),
-                                      finish(a, acc.z, old.z, i, c + 2), finish(a, acc.w, old.w, i, c + 3));
+                    __stcs(cp, make_float4(finish(a, acc.x, old.x, i, c), finish(a, acc.y, old.y, i, c + 1),
+                                           finish(a, acc.z, old.z, i, c + 2), finish(a, acc.w, old.w, i, c + 3)));
                 }
             }
             acc = make_float4(0.f, 0.f, 0.f, 0.f);
