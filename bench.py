@@ -26,7 +26,12 @@ for _p in (ROOT, PKG):
 import torch  # noqa: E402
 
 METRIC, UNIT = 'gcn_epoch_ms', 'ms'
-DRAM_BYTES_PER_ENTRY_FLOAT = 1.57    # measured DRAM traffic of a product per (stored entry x float of width), see roofline
+# DRAM traffic of the local products (dram__bytes_read + dram__bytes_write, ncu, one pass, --clock-control none):
+#   the N = 1 default workload itself, one epoch of `bench.py --steps 1 --warmup 3 --no-cpu-baseline --profiler-range`:
+#   128.18 GB for 147.87 G (stored entry x float) = 0.867 B each;
+#   the 8 products of one distributed SpMM of rank 0 of 8 at F = 256 (spmm_sweep.py --block-of 8): 6.41 GB for 4.02 G = 1.594 B each.
+MEASURED_TRAFFIC = {('sparse2m', 1, 3): 128.18e9}     # (config, ranks, layers) -> bytes per step, captured on that very workload
+TRAFFIC_PER_ENTRY_FLOAT = {'whole_graph': 0.867, 'stage_blocks': 1.594}
 
 
 def parse():
@@ -269,6 +274,7 @@ def run_ours(args):
     slow = max(gathered, key=lambda p: p['spmm_ms'])
     launches = sum(int(p['kernel_launches']) + int(p.get('dense_launches', 0)) for p in gathered)   # SpMM + dense kernels of this library
     peaks = load_peaks()
+    traffic = MEASURED_TRAFFIC.get((args.config, world, cfg['layers'])) if args.rep == 1 else None
     achieved = slow['alg_bytes'] / (slow['spmm_ms'] * 1e-3) / 1e9 if slow['spmm_ms'] > 0 else 0.0
     line = {
         'metric': METRIC, 'value': round(ms_total / args.steps, 4), 'unit': UNIT, 'n_gpus': world, 'steps': args.steps,
@@ -280,12 +286,15 @@ def run_ours(args):
                 'value_is': 'mean over the K timed epochs (one event pair around all of them), max over ranks'},
         'roofline': {'bound': 'hbm', 'achieved': round(achieved, 2), 'peak': peaks['hbm_gbs'], 'unit': 'GB/s',
                      'frac': round(achieved / peaks['hbm_gbs'], 4),
-                     # ncu on the 1 M-node / degree-48 / F=256 product: 20.65 GB of DRAM traffic for 51.38 M entries x 256
-                     # floats = 1.57 B per (entry x float); scaled here by this run's sum of nnz x F (= flops / 2), per step
-                     'traffic': round(DRAM_BYTES_PER_ENTRY_FLOAT * slow['flops'] / 2 / args.steps),
-                     'traffic_source': 'scaled from profiles/k_spmm_rows_v4_rmat1m_deg48_f256.md by nnz x F; per step, all products',
+                     # measured DRAM bytes of all products of one step where this very workload was captured under ncu, else
+                     # null with an estimate beside it: captured bytes per (stored entry x float) x this run's nnz x F (= flops / 2)
+                     'traffic': traffic,
+                     'traffic_est': round(TRAFFIC_PER_ENTRY_FLOAT['whole_graph' if world == 1 else 'stage_blocks'] * slow['flops'] / 2 / args.steps),
+                     'traffic_note': ('traffic: ncu dram__bytes of this workload\'s products, one epoch; ' if traffic else 'traffic: no capture of this workload; ')
+                                     + 'traffic_est: captured bytes per (stored entry x float) of '
+                                     + ('the whole-graph products' if world == 1 else 'the 8-rank stage-block products at F = 256') + ' x this run\'s nnz x F',
                      'peak_source': peaks['source'],
-                     'kernel': 'k_spmm_rows_v4 + k_spmm_chunks_v4 (+ generic row kernels for odd widths), all local products of the slowest rank',
+                     'kernel': 'k_spmm_v4 (+ generic row kernels for narrow widths on long rows) + k_spmm_heavy_finish, all local products of the slowest rank',
                      'products_per_step': slow['products'] // args.steps, 'spmm_ms_per_step': round(slow['spmm_ms'] / args.steps, 4),
                      'alg_bytes_per_step': slow['alg_bytes'] / args.steps,
                      'gather_gbs': round(slow['gather_bytes'] / (slow['spmm_ms'] * 1e-3) / 1e9, 2) if slow['spmm_ms'] > 0 else 0.0,

@@ -280,8 +280,7 @@ int peer_loop(dg_comm* comm, dg_comm* row_comm, const PeerPacks& packs, int32_t 
     DG_CUDA(cudaStreamWaitEvent(comm->side, comm->ev_input, 0));
     DG_NCCL(ncclAllReduce(comm->peer_token, comm->peer_token, 1, ncclFloat, ncclMax, comm->comm, comm->side));
     DG_CUDA(cudaEventRecord(comm->ev_barrier, comm->side));
-    static const int lanes_env = [] { const char* v = getenv("DG_PEER_LANES"); return v ? atoi(v) : 0; }();
-    const int lanes = lanes_env > 0 ? (lanes_env > 8 ? 8 : lanes_env) : 2;
+    const int lanes = 2;                                          // pieces of a block in flight side by side (measured best of 1, 2, 4)
     int issued = 0;                                               // copies of stages [0, issued) are on the side stream
     for (int p = 0; p < n_products; ++p) {
         if (timed) DG_CUDA(cudaEventRecord(comm->t_comm[2 * p], comm->side));

@@ -341,11 +341,11 @@ __global__ void __launch_bounds__(256, DG_V4_MIN_BLOCKS) k_spmm_v4(const SpmmArg
         const int64_t e0 = __ldg(a.rowptr + i);
         const int64_t len = __ldg(a.rowptr + i + 1) - e0;
         if (len <= a.heavy_threshold) {
+            float4* cp = reinterpret_cast<float4*>(a.C + (size_t)i * (size_t)a.ldc) + vec0;
+            float4 old = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (on && a.beta != 0.f) old = __ldcs(cp);          // requested before the gather; streams through, must not displace rows of B in L2
             gather_v4<U>(bl, ld4, a.col + e0 + lane, a.val + e0 + lane, (int)len, on, acc);
             if (on) {
-                float4* cp = reinterpret_cast<float4*>(a.C + (size_t)i * (size_t)a.ldc) + vec0;
-                float4 old = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (a.beta != 0.f) old = __ldcs(cp);            // the result streams through: it must not displace rows of B in L2
                 if constexpr (PLAIN) {
                     __stcs(cp, make_float4(fmaf(a.beta, old.x, acc.x), fmaf(a.beta, old.y, acc.y), fmaf(a.beta, old.z, acc.z),
                                            fmaf(a.beta, old.w, acc.w)));

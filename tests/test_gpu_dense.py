@@ -10,7 +10,7 @@ TOL = 1e-5
 
 
 @pytest.mark.parametrize('M,K,N', [(128, 32, 16), (128, 256, 256), (1000, 256, 256), (300, 100, 256), (129, 256, 47),
-                                   (5000, 32, 16), (77, 8, 8), (4096, 256, 128), (513, 100, 47)])
+                                   (5000, 32, 16), (77, 8, 8), (4096, 256, 128), (513, 100, 47), (400000, 256, 256)])
 def test_dense_nt_matches_float64(M, K, N):
     import spmm_cpp
     g = torch.Generator(device='cuda').manual_seed(M + K + N)
