@@ -45,7 +45,7 @@ def parse():
     ap.add_argument('--layers', type=int, default=0, help='override the number of GCN layers')
     ap.add_argument('--seed', type=int, default=0)
     ap.add_argument('--stage-group', default=None, help='stages fused into one product: a number, or for peer_compact a size list such as 4,2,1 (default: that of DistEnv)')
-    ap.add_argument('--stage-order', default=None, choices=['reference', 'local_first', 'feature_chunks', 'peer_copy', 'peer_compact'],
+    ap.add_argument('--stage-order', default=None, choices=['reference', 'local_first', 'feature_chunks', 'peer_copy', 'peer_compact', 'peer_gather'],
                     help='order of the products inside a distributed SpMM (default: that of DistEnv)')
     ap.add_argument('--chunk-width', type=int, default=0, help='column chunk width of the feature_chunks order (0 = default 64)')
     ap.add_argument('--dense', default=None, choices=['fp32', '3xtf32', 'tcgen05'],
@@ -345,8 +345,8 @@ def measure_stage_loops(env, g, widths, spmm_cpp):
         comm_ms, spmm_ms, total_ms = vals.tolist()
         received = sum(1 for st in stages if st.root_in_group != env.col_comm.rank) * n * width * 4
         moved = received if env.stage_order == 'peer_copy' else len(stages) * n * width * 4     # peer copies move remote blocks only
-        if env.stage_order == 'peer_compact' and env.rep == 1:
-            moved = received = sum(gcn_module.compact_exchange(env, g.adj_parts, stages)['stage_rows']) * width * 4
+        if env.stage_order in ('peer_compact', 'peer_gather') and env.rep == 1:
+            moved = received = sum(gcn_module.compact_exchange(env, g.adj_parts, stages, owner_packs=env.stage_order == 'peer_compact')['stage_rows']) * width * 4
         out[f'F{true_width}'] = {
             'width_on_the_wire': width,
             'bcast_bus_gbs': round(moved / (comm_ms * 1e-3) / 1e9, 2) if comm_ms > 0 else None,

@@ -81,6 +81,8 @@ int dg_spmm_launch(const dg_plan* plan, const float* val, const float* B, int64_
 int dg_spmm_launch_rows(const dg_plan* plan, const float* val, const float* B, int64_t ldb, float* C, int64_t ldc,
                         int32_t F, float alpha, float beta, uint32_t flags, const float* row_scale, const float* bias,
                         float* scratch, cudaStream_t stream);
+int dg_plan_build(const int32_t* row, const int32_t* col, int64_t nnz, int32_t m, int32_t k, int32_t heavy_threshold,
+                  int32_t chunk, bool lean, void* stream, dg_plan** out);
 int dg_spmm_prepare(const dg_plan* plan, int32_t F, cudaStream_t stream);
 int dg_check_spmm_args(const dg_plan* plan, const float* val, const float* B, int64_t ldb, const float* C, int64_t ldc,
                        int32_t F, uint32_t flags, const float* row_scale, const float* bias);

@@ -180,8 +180,10 @@ extern "C" int dg_plan_device_status(const dg_plan* p, int* host_status, void* s
     return DG_OK;
 }
 
-extern "C" int dg_plan_create_ex(const int32_t* row, const int32_t* col, int64_t nnz, int32_t m, int32_t k,
-                                 int32_t heavy_threshold, int32_t chunk, void* stream_, dg_plan** out)
+// lean: a plan that will serve one product and be destroyed (dg_spmm_coo): the distinct-column census (statistics only)
+// and the task tables of the streaming kernel are left out; touched_columns then reads k.
+int dg_plan_build(const int32_t* row, const int32_t* col, int64_t nnz, int32_t m, int32_t k, int32_t heavy_threshold,
+                  int32_t chunk, bool lean, void* stream_, dg_plan** out)
 {
     if (!out) return DG_ERR_NULL;
     *out = nullptr;
@@ -228,7 +230,7 @@ extern "C" int dg_plan_create_ex(const int32_t* row, const int32_t* col, int64_t
 
     if (m > 0) k_row_census<<<(m + T - 1) / T, T, 0, stream>>>(p->rowptr, m, heavy_threshold, d_heavy, capacity, d_nheavy,
                                                              d_counters, d_counters + 1);
-    if (nnz > 0) {
+    if (nnz > 0 && !lean) {
         const unsigned blocks = (unsigned)std::min<int64_t>((nnz + T - 1) / T, 148 * 16);
         k_mark_columns<<<blocks, T, 0, stream>>>(col, nnz, d_bitmap);
         k_count_bits<<<(unsigned)std::min<int64_t>((words + T - 1) / T, 148 * 8), T, 0, stream>>>(d_bitmap, words, d_counters + 2);
@@ -241,7 +243,7 @@ extern "C" int dg_plan_create_ex(const int32_t* row, const int32_t* col, int64_t
         return fail(rc);
     p->max_row_nnz = (int64_t)h_counters[0];
     p->heavy_nnz = (int64_t)h_counters[1];
-    p->touched_columns = (int64_t)h_counters[2];
+    p->touched_columns = lean ? (int64_t)k : (int64_t)h_counters[2];
     if (h_nheavy > capacity) return fail(DG_ERR_STATE);   // cannot happen: every heavy row holds > threshold entries
 
     if (h_nheavy > 0) {
@@ -286,9 +288,15 @@ extern "C" int dg_plan_create_ex(const int32_t* row, const int32_t* col, int64_t
         }
     }
     if ((rc = (int)cudaMalloc((void**)&p->status, sizeof(int))) || (rc = (int)cudaMemset(p->status, 0, sizeof(int)))) return fail(rc);
-    if ((rc = build_tasks(p, DG_DEFAULT_TASK_NNZ, stream))) return fail(rc);
+    if (!lean && (rc = build_tasks(p, DG_DEFAULT_TASK_NNZ, stream))) return fail(rc);
     *out = p;
     return DG_OK;
+}
+
+extern "C" int dg_plan_create_ex(const int32_t* row, const int32_t* col, int64_t nnz, int32_t m, int32_t k,
+                                 int32_t heavy_threshold, int32_t chunk, void* stream, dg_plan** out)
+{
+    return dg_plan_build(row, col, nnz, m, k, heavy_threshold, chunk, false, stream, out);
 }
 
 extern "C" int dg_plan_create(const int32_t* row, const int32_t* col, int64_t nnz, int32_t m, int32_t k, void* stream,

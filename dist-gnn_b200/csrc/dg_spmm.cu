@@ -566,7 +566,7 @@ extern "C" int dg_spmm_coo(const int32_t* row, const int32_t* col, const float* 
                            const float* B, float* C, int32_t F, float alpha, float beta, void* stream)
 {
     dg_plan* plan = nullptr;
-    int rc = dg_plan_create(row, col, nnz, m, k, stream, &plan);
+    int rc = dg_plan_build(row, col, nnz, m, k, 0, 0, /*lean=*/true, stream, &plan);
     if (rc) return rc;
     rc = dg_spmm_csr(plan, val, B, F, C, F, F, alpha, beta, 0u, nullptr, nullptr, stream);
     if (rc == DG_OK) rc = (int)cudaStreamSynchronize((cudaStream_t)stream);   // the plan's buffers die below

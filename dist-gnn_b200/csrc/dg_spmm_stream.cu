@@ -221,12 +221,6 @@ __global__ void __launch_bounds__(128) k_stream_fixup(const StreamArgs a)
     }
 }
 
-int env_int(const char* name, int fallback)
-{
-    const char* e = std::getenv(name);
-    return e && *e ? std::atoi(e) : fallback;
-}
-
 struct Tuning {
     int choice;     // 0 automatic, 1 row kernels only, 2 streaming whenever eligible
     int stages;     // ring depth: 2, 4 or 8
@@ -240,9 +234,9 @@ Tuning& tuning()
         Tuning v{};
         const char* e = std::getenv("DG_SPMM_KERNEL");
         v.choice = !e ? 0 : !std::strcmp(e, "rows") ? 1 : !std::strcmp(e, "stream") ? 2 : 0;
-        v.stages = env_int("DG_STREAM_STAGES", 2);
-        v.rps = env_int("DG_STREAM_RPS", 0);
-        v.warps = env_int("DG_STREAM_WARPS", 0);
+        v.stages = 2;       // ring depth, entries per stage and warps per CTA: the measured best; 0 = derived from the row width
+        v.rps = 0;
+        v.warps = 0;
         return v;
     }();
     return t;

@@ -43,12 +43,14 @@ class DistEnv:
         # 'feature_chunks' (1D): all-gather the operand one column chunk at a time, one full-row product per chunk;
         # 'peer_copy':   own block first, remote blocks pulled from their owners' send buffers by device-to-device copies.
         # 'peer_compact': peer_copy that moves only the operand rows each reader's sparse block touches (1D; less than half
-        #                of the rows at 8 ranks on the benchmark graph).
+        #                of the rows at 8 ranks on the benchmark graph): the owner packs them per reader, the reader copies.
+        # 'peer_gather':  the same rows, gathered by the reader out of the owner's whole block with a small pull kernel; the
+        #                owners pack nothing and nothing is exchanged beforehand.
         # Default: peer_compact for 1D (2 GPUs: 37.8 ms against 38.6 for peer_copy and 48.2 for 'reference'; peer_copy at 8
         # GPUs: 25.4 against 27.4, with 0.8-0.9 of the transfer hidden), reference for 1.5D (peer copies were slower there).
         default_order = 'peer_compact' if rep == 1 else 'reference'
         self.stage_order = stage_order if stage_order is not None else os.environ.get('DIST_GNN_STAGE_ORDER', default_order)
-        if self.stage_order not in ('reference', 'local_first', 'feature_chunks', 'peer_copy', 'peer_compact'):
+        if self.stage_order not in ('reference', 'local_first', 'feature_chunks', 'peer_copy', 'peer_compact', 'peer_gather'):
             raise ValueError(f'unknown stage order {self.stage_order!r}')
         # Stages fused into one product (1 = stage by stage, as the reference).  Peer copies and 1.5D run stage by stage;
         # the broadcast loop of 1D is fastest with two products per distributed SpMM (half of the stages each): longer

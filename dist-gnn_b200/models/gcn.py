@@ -147,7 +147,19 @@ def _stage_loop(env, local_adj_parts, x, z, stages, comm, timed=False):
         with env.timer.timing_cuda('broadcast+spmm'):
             spmm_cpp.allgather_spmm(comm, plan, x, pack, area, z, widths, timed=timed)
         return z
-    if comm is not None and env.stage_order == 'peer_compact' and env.rep == 1:
+    if comm is not None and env.stage_order == 'peer_gather' and env.rep == 1 and width % 4 == 0:
+        ex = compact_exchange(env, local_adj_parts, stages, owner_packs=False)
+        if env.ensure_peer_buffers(n * width):
+            area = env.recv_buffers(max(ex['area_rows'], 1), width, nbuf=1, tag='compact')[0]
+            landing = [None] * len(ex['own']) + [area[o:o + r] for o, r in zip(ex['area_offsets'], ex['stage_rows'])]
+            products = [(spmm_cpp.plan_for(local_adj_parts[stages[i].part]), x, -1) for i in ex['own']]
+            products += [(plan, area[o:o + r], len(ex['own']) + last)
+                         for plan, (o, r), last in zip(ex['plans'], ex['plan_slices'], ex['plan_last'])]
+            with env.timer.timing_cuda('broadcast+spmm'):
+                spmm_cpp.peer_spmm_gather(comm, ex['roots'], [None] * len(ex['own']) + ex['lists'], [0] * len(ex['own']) + ex['stage_rows'],
+                                          landing, products, x, z, timed=timed)
+            return z
+    if comm is not None and env.stage_order in ('peer_compact', 'peer_gather') and env.rep == 1:
         ex = compact_exchange(env, local_adj_parts, stages)
         if env.ensure_peer_buffers(ex['send_rows'] * width):
             area = env.recv_buffers(max(ex['area_rows'], 1), width, nbuf=1, tag='compact')[0]
@@ -160,7 +172,7 @@ def _stage_loop(env, local_adj_parts, x, z, stages, comm, timed=False):
                 spmm_cpp.peer_spmm_packed(comm, ex['packs'], ex['roots'], zeros + ex['stage_offsets'], zeros + ex['stage_rows'], landing,
                                           products, x, z, timed=timed)
             return z
-    if comm is not None and env.stage_order in ('peer_copy', 'peer_compact') and env.ensure_peer_buffers(n * width):
+    if comm is not None and env.stage_order in ('peer_copy', 'peer_compact', 'peer_gather') and env.ensure_peer_buffers(n * width):
         with env.timer.timing_cuda('broadcast+spmm'):
             spmm_cpp.peer_spmm(comm, *ordered_products(env, local_adj_parts, stages, x, rotate=True), x, z, row_comm=env.row_comm,
                                timed=timed)
@@ -197,16 +209,21 @@ def group_sizes(count, spec):
     return sizes
 
 
-def compact_exchange(env, adj_parts, stages):
-    """One-off set-up of the 'peer_compact' stage order for this rank's blocks (1D).  For every remote block: the sorted
-    list of the columns it touches and the block with its column ids replaced by positions in that list; after one
-    exchange of the lists, where this rank's rows start inside each owner's send buffer and which rows this rank packs
-    for every reader.  The pulled lists land side by side in one area in pull order, and env.stage_group consecutive
-    arrivals are multiplied by ONE product over their joined block (column id = position inside the group's slice of the
-    area): fewer read-modify-write passes over the result and longer rows, at the price of waiting for the group's last
-    arrival.  Collective over the column communicator's ranks (an all-gather of the lists as host objects)."""
+def compact_exchange(env, adj_parts, stages, owner_packs=True):
+    """One-off set-up of the stage orders that move only the operand rows a block touches (1D).  For every remote block:
+    the sorted list of the columns it touches and the block with its column ids replaced by positions in that list.  The
+    pulled rows land side by side in one area in pull order, and env.stage_group consecutive arrivals are multiplied by
+    ONE product over their joined block (column id = position inside the group's slice of the area): fewer
+    read-modify-write passes over the result and longer rows, at the price of waiting for the group's last arrival.
+
+    owner_packs=True ('peer_compact'): the lists are exchanged once (an all-gather of host objects over the column
+    communicator's ranks), every owner then packs, per distributed SpMM, each reader's rows into its send buffer and the
+    reader pulls its list with one copy: this call also returns where this rank's rows start inside each owner's buffer
+    and which rows this rank packs for every reader.
+    owner_packs=False ('peer_gather'): nothing is exchanged; the reader gathers its rows out of the owner's whole block
+    itself, so all it needs are its own lists (kept on the device)."""
     import torch.distributed as dist
-    key = (id(adj_parts), tuple(group_sizes(len(stages), env.stage_group)))
+    key = (id(adj_parts), tuple(group_sizes(len(stages), env.stage_group)), bool(owner_packs))
     hit = _compact_cache.get(key)
     if hit is not None and hit[0] is adj_parts:
         return hit[1]
@@ -214,7 +231,7 @@ def compact_exchange(env, adj_parts, stages):
     me, size = comm.rank, comm.size
     own, remote = schedule.pull_order(stages, me, size)
     n = adj_parts[0].size(0)
-    wanted, blocks, kept = {}, [], []
+    wanted, blocks, kept, lists = {}, [], [], []
     for i in remote:
         block = adj_parts[stages[i].part]
         idx = block.indices()
@@ -222,16 +239,26 @@ def compact_exchange(env, adj_parts, stages):
             continue                                                  # an empty block adds nothing: no list, no copy, no product
         touched = torch.unique(idx[1])                                # ascending
         blocks.append((idx[0], torch.searchsorted(touched, idx[1].contiguous()), block.values(), touched.numel()))
-        wanted[stages[i].root_in_group] = touched.to(torch.int32).cpu().numpy()
+        if owner_packs:
+            wanted[stages[i].root_in_group] = touched.to(torch.int32).cpu().numpy()
+        else:
+            lists.append(touched.to(torch.int32).contiguous())
         kept.append(i)
-    gathered = [None] * size
-    dist.all_gather_object(gathered, wanted, group=env.world_group)   # gathered[q][s]: rows of block s that reader q needs
-    lay = schedule.compact_layout(gathered, me, [stages[i].root_in_group for i in kept])
-    for q, _ in lay['packs']:                                         # the rows a reader asks for must exist in this rank's block
-        ids = gathered[q][me]
-        if len(ids) and (int(ids.min()) < 0 or int(ids.max()) >= n):
-            raise RuntimeError(f'rank {q} asked rank {me} for rows outside its block of {n} rows')
-    packs = [(torch.from_numpy(gathered[q][me]).to(env.device), offset) for q, offset in lay['packs']]
+    if owner_packs:
+        gathered = [None] * size
+        dist.all_gather_object(gathered, wanted, group=env.world_group)   # gathered[q][s]: rows of block s that reader q needs
+        lay = schedule.compact_layout(gathered, me, [stages[i].root_in_group for i in kept])
+        for q, _ in lay['packs']:                                         # the rows a reader asks for must exist in this rank's block
+            ids = gathered[q][me]
+            if len(ids) and (int(ids.min()) < 0 or int(ids.max()) >= n):
+                raise RuntimeError(f'rank {q} asked rank {me} for rows outside its block of {n} rows')
+        packs = [(torch.from_numpy(gathered[q][me]).to(env.device), offset) for q, offset in lay['packs']]
+    else:
+        stage_rows = [b[3] for b in blocks]
+        offsets = [sum(stage_rows[:j]) for j in range(len(stage_rows))]
+        lay = dict(stage_rows=stage_rows, area_offsets=offsets, area_rows=sum(stage_rows), stage_offsets=[0] * len(stage_rows),
+                   send_rows=n, sizes=None)
+        packs = []
     plans, plan_slices, plan_last = [], [], []
     first = 0
     for count in group_sizes(len(kept), env.stage_group):
@@ -250,7 +277,7 @@ def compact_exchange(env, adj_parts, stages):
         plan_slices.append((base, rows_total))
         plan_last.append(first + count - 1)
         first += count
-    ex = dict(own=own, remote=kept, plans=plans, plan_slices=plan_slices, plan_last=plan_last, packs=packs,
+    ex = dict(own=own, remote=kept, plans=plans, plan_slices=plan_slices, plan_last=plan_last, packs=packs, lists=lists,
               roots=[stages[i].root_in_group for i in own + kept],
               stage_rows=lay['stage_rows'], stage_offsets=lay['stage_offsets'], area_offsets=lay['area_offsets'],
               area_rows=lay['area_rows'], send_rows=lay['send_rows'], sizes=lay['sizes'])

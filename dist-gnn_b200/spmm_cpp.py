@@ -80,6 +80,7 @@ def lib():
             'dg_comm_peer_capacity': ([vp], ctypes.c_int64),
             'dg_peer_spmm_packed': ([vp, vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, vp, ctypes.c_int, vp], ctypes.c_int),
             'dg_peer_spmm': ([vp, vp, i32, vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, vp, ctypes.c_int, vp], ctypes.c_int),
+            'dg_peer_spmm_gather': ([vp, vp, i32, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, vp, ctypes.c_int, vp], ctypes.c_int),
             'dg_dense_split': ([vp, vp, vp, i64, vp], ctypes.c_int),
             'dg_dense_supported': ([i64, i32, i32, i64, i64, vp, vp, vp], ctypes.c_int),
             'dg_dense_nt': ([vp, i64, vp, vp, i64, vp, i64, i64, i32, i32, i32, vp], ctypes.c_int),
@@ -430,6 +431,38 @@ def peer_spmm_packed(comm, packs, roots, stage_offsets, stage_rows, landing, pro
     last_arr = (ctypes.c_int32 * max(P, 1))(*[l for _, _, l in products])
     with torch.cuda.device(x_local.device):
         check(lib().dg_peer_spmm_packed(comm.handle, row_comm.handle if row_comm else None, Q, pr, pc, po, S, roots_arr, so, sr, land_arr,
+                                        P, plan_arr, val_arr, op_arr, last_arr, x_local.data_ptr(), n, F, z.data_ptr(), int(timed), _stream()))
+    return z
+
+
+def peer_spmm_gather(comm, roots, stage_lists, stage_rows, landing, products, x_local, z, row_comm=None, timed=False):
+    """dg_peer_spmm_gather: peer_spmm whose reader gathers, out of each root's whole block, only the rows its sparse block
+    touches (a small pull kernel on the side stream; the owners pack nothing).
+
+    roots[s], stage_lists[s], stage_rows[s]   root of stage s, the ascending row ids to fetch (int32 CUDA tensor; None at an
+                   own stage) and their count;  landing[s]: (stage_rows[s] x F) tensor, or None at an own stage
+    products       (plan, operand, last_stage) as for peer_spmm; the plans of remote blocks use the packed numbering"""
+    _dev_tensor(x_local, torch.float32, 'x_local'), _dev_tensor(z, torch.float32, 'z')
+    n, F = x_local.shape
+    S, P = len(roots), len(products)
+    for rows in stage_lists:
+        if rows is not None:
+            _dev_tensor(rows, torch.int32, 'stage row ids')
+    roots_arr = (ctypes.c_int32 * max(S, 1))(*roots)
+    lists_arr = (ctypes.c_void_p * max(S, 1))(*[None if t is None or t.numel() == 0 else t.data_ptr() for t in stage_lists])
+    sr = (ctypes.c_int64 * max(S, 1))(*[int(v) for v in stage_rows])
+    land_arr = (ctypes.c_void_p * max(S, 1))(*[None if t is None or t.numel() == 0 else _dev_tensor(t, torch.float32, 'landing block').data_ptr()
+                                                for t in landing])
+    for plan, operand, _ in products:
+        _dev_tensor(operand, torch.float32, 'operand')
+        if operand.size(0) != plan.k or operand.size(1) != F:
+            raise RuntimeError(f'operand {tuple(operand.shape)} does not match a plan with {plan.k} columns and width {F}')
+    plan_arr = (ctypes.c_void_p * max(P, 1))(*[p.handle for p, _, _ in products])
+    val_arr = (ctypes.c_void_p * max(P, 1))(*[p.values.data_ptr() for p, _, _ in products])
+    op_arr = (ctypes.c_void_p * max(P, 1))(*[t.data_ptr() for _, t, _ in products])
+    last_arr = (ctypes.c_int32 * max(P, 1))(*[l for _, _, l in products])
+    with torch.cuda.device(x_local.device):
+        check(lib().dg_peer_spmm_gather(comm.handle, row_comm.handle if row_comm else None, S, roots_arr, lists_arr, sr, land_arr,
                                         P, plan_arr, val_arr, op_arr, last_arr, x_local.data_ptr(), n, F, z.data_ptr(), int(timed), _stream()))
     return z
 

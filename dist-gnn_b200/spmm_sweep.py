@@ -100,8 +100,8 @@ def main():
         if world > 1:
             t = env.col_comm.last_times()
             moved = (world - 1) * n * width * 4
-            if env.stage_order == 'peer_compact':
-                moved = sum(gcn.compact_exchange(env, parts, stages)['stage_rows']) * width * 4
+            if env.stage_order in ('peer_compact', 'peer_gather'):
+                moved = sum(gcn.compact_exchange(env, parts, stages, owner_packs=env.stage_order == 'peer_compact')['stage_rows']) * width * 4
             line.update(moved_bytes=moved, bus_gbs=round(moved / (t['comm_ms'] * 1e-3) / 1e9, 2) if t['comm_ms'] > 0 else None,
                         comm_ms=round(t['comm_ms'], 4), loop_ms=round(t['total_ms'], 4), loop_spmm_ms=round(t['spmm_ms'], 4),
                         overlap=round((t['comm_ms'] + t['spmm_ms'] - t['total_ms']) / max(min(t['comm_ms'], t['spmm_ms']), 1e-9), 4))

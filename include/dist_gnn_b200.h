@@ -212,6 +212,17 @@ int dg_peer_spmm_packed(dg_comm* comm, dg_comm* row_comm, int32_t n_packs, const
                         float* const* host_landing, int32_t n_products, const dg_plan* const* host_plans,
                         const float* const* host_vals, const float* const* host_operands, const int32_t* host_last_stage,
                         const float* x_local, int32_t n, int32_t F, float* z, int timed, void* compute_stream);
+/* The same loop with the gather done by the READER: every rank publishes its whole block (as dg_peer_spmm does: send
+ * buffers of n * F floats) and packs nothing; for stage s the reader launches a small pull kernel on the side stream
+ * that copies the host_stage_rows[s] rows listed in host_stage_lists[s] (device row ids of the root's block, ascending)
+ * out of the root's send buffer into host_landing[s], with plain loads over NVLink (no multicast, no waiting on the
+ * peer: the meeting point before it made the block complete).  Plans of remote blocks use the packed numbering, as
+ * above; nothing has to be exchanged between the ranks beforehand.  F must be a multiple of 4. */
+int dg_peer_spmm_gather(dg_comm* comm, dg_comm* row_comm, int32_t n_stages, const int32_t* host_roots,
+                        const int32_t* const* host_stage_lists, const int64_t* host_stage_rows, float* const* host_landing,
+                        int32_t n_products, const dg_plan* const* host_plans, const float* const* host_vals,
+                        const float* const* host_operands, const int32_t* host_last_stage, const float* x_local, int32_t n,
+                        int32_t F, float* z, int timed, void* compute_stream);
 /* 1D only: the same distributed product pipelined along the feature dimension (replaces gcn.py:16-30 as a whole).  The
  * n x F operand is cut into n_chunks column chunks (host_chunk_widths, summing to F).  Chunk c of every rank is
  * all-gathered on the side stream into host_area[c % 2] ((nranks*n) x w_c, rank r's rows at r*n) while the compute

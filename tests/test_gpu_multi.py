@@ -69,6 +69,10 @@ def _worker(rank, world, rep, port, out_dir, mode):
                 rec[f'zc{i}'] = broadcast(g.adj_parts, x, f'w{width}').cpu().numpy()
                 env.stage_group = (3, 2, 1)                             # the same with arrivals joined into fewer products
                 rec[f'zcg{i}'] = broadcast(g.adj_parts, x, f'w{width}').cpu().numpy()
+                env.stage_group, env.stage_order = 1, 'peer_gather'     # the reader gathers its rows out of the owner's whole block
+                rec[f'zq{i}'] = broadcast(g.adj_parts, x, f'w{width}').cpu().numpy()
+                env.stage_group = (2, 1)
+                rec[f'zqg{i}'] = broadcast(g.adj_parts, x, f'w{width}').cpu().numpy()
                 env.stage_group, env.stage_order = 1, 'reference'
         torch.cuda.synchronize()
         np.savez(os.path.join(out_dir, f'rank{rank}.npz'), **rec)
@@ -113,7 +117,7 @@ def test_back_to_back_stage_loops_at_two_ranks(golden):
         want = ref_gcn.broadcast_1d([p['adj_parts'] for p in parts], [res[r][f'x{i}'] for r in range(2)])
         for r in range(2):
             assert_close(res[r][f'z{i}'], want[r], 1e-5, f'loop {i} rank {r}')
-            for key in ('zg', 'zl', 'zlg', 'zf', 'zp', 'zpg', 'zc', 'zcg'):
+            for key in ('zg', 'zl', 'zlg', 'zf', 'zp', 'zpg', 'zc', 'zcg', 'zq', 'zqg'):
                 assert_close(res[r][f'{key}{i}'], want[r], 1e-5, f'{key} loop {i} rank {r}')
 
 
@@ -126,7 +130,7 @@ def test_15d_stage_loop_at_four_ranks(golden):
         want = ref_gcn.broadcast_15d([p['adj_parts'] for p in parts], [res[b * 2][f'x{i}'] for b in range(2)], 4, 2)
         for r in range(4):
             assert_close(res[r][f'z{i}'], want[r], 1e-5, f'loop {i} rank {r}')
-            for key in ('zg', 'zl', 'zlg', 'zf', 'zp', 'zpg', 'zc', 'zcg'):
+            for key in ('zg', 'zl', 'zlg', 'zf', 'zp', 'zpg', 'zc', 'zcg', 'zq', 'zqg'):
                 assert_close(res[r][f'{key}{i}'], want[r], 1e-5, f'{key} loop {i} rank {r}')
 
 
@@ -138,7 +142,7 @@ def test_every_1d_schedule_at_eight_ranks(golden):
     for i in range(4):
         want = ref_gcn.broadcast_1d([p['adj_parts'] for p in parts], [res[r][f'x{i}'] for r in range(8)])
         for r in range(8):
-            for key in ('z', 'zg', 'zl', 'zlg', 'zf', 'zp', 'zpg', 'zc', 'zcg'):
+            for key in ('z', 'zg', 'zl', 'zlg', 'zf', 'zp', 'zpg', 'zc', 'zcg', 'zq', 'zqg'):
                 assert_close(res[r][f'{key}{i}'], want[r], 1e-5, f'{key} loop {i} rank {r}')
 
 
@@ -150,7 +154,7 @@ def test_15d_stage_loop_at_eight_ranks(golden):
     for i in range(4):
         want = ref_gcn.broadcast_15d([p['adj_parts'] for p in parts], [res[b * 2][f'x{i}'] for b in range(4)], 8, 2)
         for r in range(8):
-            for key in ('z', 'zg', 'zl', 'zlg', 'zf', 'zp', 'zpg', 'zc', 'zcg'):
+            for key in ('z', 'zg', 'zl', 'zlg', 'zf', 'zp', 'zpg', 'zc', 'zcg', 'zq', 'zqg'):
                 assert_close(res[r][f'{key}{i}'], want[r], 1e-5, f'{key} loop {i} rank {r}')
 
 
