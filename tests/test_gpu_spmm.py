@@ -53,6 +53,42 @@ def test_golden_cases_through_the_drop_in_signature(golden):
         assert_close(C.cpu().numpy(), g('C'), TOL, name)
 
 
+def test_drop_in_route_keeps_plans_only_for_the_same_matrix():
+    """spmm_cusparse recognises a block by the address of its values and re-checks the ids it is given: the same block
+    again reuses the plan (fresh int32 copies of the ids, as the reference's binding passes them), other ids at the same
+    values address build a new one, and the transient-plan route (cache off) gives the same numbers."""
+    import spmm_cpp
+    rng = np.random.Generator(np.random.PCG64(91))
+    A = random_coo(rng, 200, 150, 3000, heavy=[(9, 140)])
+    B = rng.standard_normal((150, 36), dtype=np.float32)
+    C0 = rng.standard_normal((200, 36), dtype=np.float32)
+    want = ref_gcn.spmm_coo(A, B, C0.copy(), 1.0, 1.0)
+    row, col, val = dev(A.row, torch.int32), dev(A.col, torch.int32), dev(A.val)
+    spmm_cpp._dropin_plans.clear()
+    for _ in range(3):
+        C = dev(C0)
+        spmm_cpp.spmm_cusparse(row.clone(), col.clone(), val, 200, 150, dev(B), C, 1, 1)
+        assert_close(C.cpu().numpy(), want, TOL, 'drop-in, cached plan')
+    assert len(spmm_cpp._dropin_plans) == 1
+    first_plan = next(iter(spmm_cpp._dropin_plans.values()))[0]
+    # another matrix whose values live at the same address: same nnz and shape, rows reversed
+    A2 = ref_graph.fast_coalesce_sorted((199 - A.row).astype(np.int64), A.col.astype(np.int64), A.val, (200, 150))
+    val.copy_(dev(A2.val))
+    C = dev(C0)
+    spmm_cpp.spmm_cusparse(dev(A2.row, torch.int32), dev(A2.col, torch.int32), val, 200, 150, dev(B), C, 1, 1)
+    assert_close(C.cpu().numpy(), ref_gcn.spmm_coo(A2, B, C0.copy(), 1.0, 1.0), TOL, 'drop-in after the matrix changed')
+    assert len(spmm_cpp._dropin_plans) == 1 and next(iter(spmm_cpp._dropin_plans.values()))[0] is not first_plan
+    keep = spmm_cpp.DROPIN_PLAN_CACHE
+    try:
+        spmm_cpp.DROPIN_PLAN_CACHE = 0
+        C = dev(C0)
+        spmm_cpp.spmm_cusparse(dev(A2.row, torch.int32), dev(A2.col, torch.int32), val, 200, 150, dev(B), C, 1, 1)
+        assert_close(C.cpu().numpy(), ref_gcn.spmm_coo(A2, B, C0.copy(), 1.0, 1.0), TOL, 'drop-in, transient plan')
+    finally:
+        spmm_cpp.DROPIN_PLAN_CACHE = keep
+        spmm_cpp._dropin_plans.clear()
+
+
 @pytest.mark.parametrize('F', [1, 2, 3, 4, 6, 8, 10, 16, 20, 32, 41, 47, 64, 100, 128, 130, 256, 300, 512, 602, 1024])
 def test_widths_against_oracle(F):
     rng = np.random.Generator(np.random.PCG64(F))
