@@ -7,7 +7,10 @@
 A step is one training epoch as light_dist_gnn/dist_train.py:36-45 runs it: forward through the L DistGCNLayers
 (2L distributed SpMMs per epoch counting backward), cross-entropy over the local train rows, backward, Adam.  The
 graph, labels and split are regenerated from a seed on every rank (integer hash, identical everywhere); the same
-total problem is split over N ranks, so scaling is "strong".  Rank 0 prints ONE JSON line.
+total problem is split over N ranks, so scaling is "strong".  Rank 0 prints ONE JSON line.  Beside the contract's keys it
+carries `parity` (the distributed product of the active schedule against a float64 evaluation of sampled rows; the run
+exits non-zero above 1e-5), `reuse` (the same epochs with the constant first-layer product kept), `comm` (N > 1) and
+`run` (schedule, median epoch).  `--impl reference` runs the unmodified reference from baseline/_ref over gloo.
 """
 import argparse
 import json
