@@ -261,7 +261,9 @@ def run_ours(args):
     cached_ms = timed_epochs(args.steps)
     model.input_gradient_shortcut = True
     shortcut_ms = timed_epochs(args.steps)
-    model.cache_input_product = model.input_gradient_shortcut = False
+    model.transform_first = True
+    all_ms = timed_epochs(args.steps)
+    model.cache_input_product = model.input_gradient_shortcut = model.transform_first = False
     model._product = None
     # ---- per-stage-loop communication numbers (N > 1): one timed distributed SpMM per width ---------------------------
     comm_info = None
@@ -309,8 +311,10 @@ def run_ours(args):
     }
     line['parity'] = parity
     line['reuse'] = {'cached_input_product_ms': round(cached_ms, 4), 'with_gradient_shortcut_ms': round(shortcut_ms, 4),
-                     'note': 'same epochs with the first layer\'s A X kept between epochs (bit-identical losses), and with its weight '
-                             'gradient also taken from that product (equal up to rounding for a symmetric adjacency); `value` recomputes both'}
+                     'with_transform_first_ms': round(all_ms, 4),
+                     'note': 'same epochs with the first layer\'s A X kept between epochs (bit-identical losses); then with its weight '
+                             'gradient also taken from that product (equal up to rounding for a symmetric adjacency); then with the last '
+                             'layer computed as A (H W) too (47-wide stage loop, equal up to rounding); `value` uses none of them'}
     if comm_info is not None:
         line['comm'] = comm_info
     if world == 1 and rank == 0 and not args.no_cpu_baseline:

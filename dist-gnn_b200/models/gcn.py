@@ -360,13 +360,24 @@ class DistGCNLayer(torch.autograd.Function):
                     product^T * grad_output instead of X^T * (A * grad_output), which skips the backward stage loop too.
                     Summed over the ranks the two are the same matrix when A is symmetric - the assumption the reference
                     already makes by multiplying with the un-transposed row block in backward (gcn.py:47) - but each
-                    rank's term, and the rounding, differ."""
+                    rank's term, and the rounding, differ.
+    transform_first for a layer without ReLU whose output is narrower than its input (the last one: 256 -> 47), compute
+                    A (X W) instead of (A X) W: the stage loop then runs at the output width.  Same result up to rounding,
+                    same backward pass."""
 
     @staticmethod
-    def forward(ctx, features, weight, adj_parts, tag, relu=False, input_is_relu=False, product=None, shortcut=False):
+    def forward(ctx, features, weight, adj_parts, tag, relu=False, input_is_relu=False, product=None, shortcut=False,
+                transform_first=False):
         ctx.adj_parts, ctx.tag, ctx.input_is_relu = adj_parts, tag, input_is_relu
         ctx.weight_key = weight                      # the caller's tensor object: key of the split-weight cache
         ctx.shortcut = bool(shortcut and product is not None)
+        if transform_first and product is None and not relu and weight.size(1) < features.size(1):
+            # A (X W) instead of (A X) W: the same matrix up to rounding, with the distributed SpMM at the narrower output
+            # width.  The backward pass below is unchanged: AG = A G, dX = AG W^T and dW = X^T AG are what both orders need.
+            ctx.save_for_backward(features, weight)
+            with DistEnv.env.timer.timing_cuda('mm'):
+                y = dense_mm(features, weight, weight_key=weight)
+            return broadcast(adj_parts, y, 'Forward' + tag)
         z_local = product if product is not None else broadcast(adj_parts, features, 'Forward' + tag)
         ctx.save_for_backward(z_local if ctx.shortcut else features, weight)
         with DistEnv.env.timer.timing_cuda('mm'):
@@ -381,7 +392,7 @@ class DistGCNLayer(torch.autograd.Function):
                 grad_weight = dense_mm(features, grad_output, ta=True, constant_a=True)      # `features` holds the saved product here
             with DistEnv.env.timer.timing_cuda('all_reduce'):
                 DistEnv.env.all_reduce_sum(grad_weight)
-            return None, grad_weight, None, None, None, None, None, None
+            return None, grad_weight, None, None, None, None, None, None, None
         if ctx.shortcut:
             raise RuntimeError('the gradient shortcut needs an input that requires no gradient')
         ag = broadcast(ctx.adj_parts, grad_output, 'Backward' + ctx.tag)
@@ -392,7 +403,7 @@ class DistGCNLayer(torch.autograd.Function):
             grad_weight = dense_mm(features, ag, ta=True, constant_a=not ctx.needs_input_grad[0])
         with DistEnv.env.timer.timing_cuda('all_reduce'):
             DistEnv.env.all_reduce_sum(grad_weight)
-        return grad_features, grad_weight, None, None, None, None, None, None
+        return grad_features, grad_weight, None, None, None, None, None, None, None
 
 
 class GCN(nn.Module):
@@ -408,13 +419,17 @@ class GCN(nn.Module):
     input_gradient_shortcut with the cache, also take the first layer's weight gradient from the cached product (see
                             DistGCNLayer `shortcut`): no stage loop at all for layer 1.  Equal to the reference's
                             gradient for a symmetric adjacency up to rounding, not bit for bit.
-    Both are off by default: the like-for-like epoch recomputes everything, as the reference does."""
+    transform_first         the last layer multiplies by its weight before the stage loop when that is the narrower side
+                            (DistGCNLayer `transform_first`): a 47-wide distributed SpMM instead of a 256-wide one.
+    All are off by default: the like-for-like epoch computes what the reference computes, in its order."""
 
-    def __init__(self, g, env, hidden_dim=16, num_layers=3, weights=None, cache_input_product=False, input_gradient_shortcut=False):
+    def __init__(self, g, env, hidden_dim=16, num_layers=3, weights=None, cache_input_product=False, input_gradient_shortcut=False,
+                 transform_first=False):
         super().__init__()
         self.g, self.env, self.num_layers = g, env, num_layers
         self.cache_input_product = bool(cache_input_product or input_gradient_shortcut)
         self.input_gradient_shortcut = bool(input_gradient_shortcut)
+        self.transform_first = bool(transform_first)
         self._product = None        # (features tensor, its version, the cached product)
         in_dim, out_dim = g.features.size(1), g.num_classes
         dims = [in_dim] + [hidden_dim] * (num_layers - 1) + [out_dim]
@@ -447,9 +462,10 @@ class GCN(nn.Module):
             product = self.input_product(h) if l == 0 else None
             shortcut = self.input_gradient_shortcut and product is not None
             if FUSE_RELU:
-                h = DistGCNLayer.apply(h, w, self.g.adj_parts, f'L{l + 1}', l < last, l > 0, product, shortcut)
+                h = DistGCNLayer.apply(h, w, self.g.adj_parts, f'L{l + 1}', l < last, l > 0, product, shortcut, self.transform_first)
             else:
-                h = DistGCNLayer.apply(h, w, self.g.adj_parts, f'L{l + 1}', False, False, product, shortcut)
+                h = DistGCNLayer.apply(h, w, self.g.adj_parts, f'L{l + 1}', False, False, product, shortcut,
+                                       self.transform_first and l == last)
                 if l < last:
                     h = F.relu(h)
         return h

@@ -333,3 +333,21 @@ def test_input_gradient_shortcut_matches_within_rounding(golden, env1):
         assert abs(a - b) <= 2e-5 * max(1.0, abs(a))
     for a, b in zip(plain_model.weights(), short_model.weights()):
         assert_close(b.detach().cpu().numpy(), a.detach().cpu().numpy(), 1e-4, 'weights with the gradient shortcut')
+
+
+def test_transform_first_matches_within_rounding(golden, env1):
+    """GCN(transform_first=True): the last layer computes A (H W) instead of (A H) W, so its stage loop runs at the class
+    count instead of the hidden width.  Same losses within 2e-5, same weights after 4 steps within 1e-4; the backward pass
+    is the same computation."""
+    import dist_train
+    from coo_graph import COO_Graph, Parted_COO_Graph
+    z = golden('graph_small')
+    g = Parted_COO_Graph.from_full(COO_Graph.from_dict('gsmall', _fixture_dataset(z), device='cuda'), 0, 1)
+    plain_model, plain = dist_train.train(g, env1, total_epoch=4, hidden_dim=16, num_layers=3)
+    first_model, first = dist_train.train(g, env1, total_epoch=4, hidden_dim=16, num_layers=3, transform_first=True)
+    for a, b in zip(plain, first):
+        assert abs(a - b) <= 2e-5 * max(1.0, abs(a))
+    for a, b in zip(plain_model.weights(), first_model.weights()):
+        assert_close(b.detach().cpu().numpy(), a.detach().cpu().numpy(), 1e-4, 'weights with transform_first')
+    with torch.no_grad():
+        assert_close(first_model(g.features).cpu().numpy(), plain_model(g.features).cpu().numpy(), 1e-4, 'outputs')
