@@ -303,7 +303,9 @@ int peer_loop(dg_comm* comm, dg_comm* row_comm, const PeerPacks& packs, int32_t 
     if (timed) DG_CUDA(cudaEventRecord(comm->t_begin, compute));
     if (n_products == 0 && count) DG_CUDA(cudaMemsetAsync(z, 0, count * sizeof(float), compute));
     const int b = (int)(comm->peer_loops & 1);
-    // this rank's block goes where its peers can read it; everything queued so far on the compute stream comes first
+    // this rank's block goes where its peers can read it; everything queued so far on the compute stream comes first.
+    // (Packing on the side stream instead, beside the rank's own product, was measured neutral on 2 and 4 GPUs - the product
+    // slows down by what the pack no longer costs in front of it - and a warp-per-row pack kernel was no faster.)
     if (packed) {
         for (int q = 0; q < packs.n_packs && count; ++q) {
             if (packs.counts[q] == 0) continue;
