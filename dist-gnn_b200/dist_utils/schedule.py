@@ -93,3 +93,24 @@ def compact_layout(gathered, me, remote_roots):
         total += rows
     return dict(sizes=sizes, packs=packs, stage_offsets=[layouts[r][0][me] for r in remote_roots], stage_rows=stage_rows,
                 area_offsets=area_offsets, area_rows=total, send_rows=max(max(t for _, t in layouts), 1))
+
+
+def join_packed_blocks(blocks, area_offsets, first, count):
+    """The sparse block of ONE product that multiplies `count` consecutive arrivals of the compact peer loops.
+    blocks[j] = (row ids, packed column ids, values, rows of the packed operand) of arrival j (torch tensors; the
+    column ids are positions in that arrival's own list); area_offsets[j] = first row of arrival j in the landing area.
+    Returns (row, col, val, operand rows): column ids re-based to the group's slice of the area (arrival `first` starts
+    at 0), entries in row-major order and, inside a row, ascending (arrival, column) - the order a stage-by-stage loop
+    would add them in."""
+    import torch
+    members = range(first, first + count)
+    base = area_offsets[first]
+    total = sum(blocks[j][3] for j in members)
+    if count == 1:
+        row, col, val, _ = blocks[first]
+        return row, col, val, total
+    row = torch.cat([blocks[j][0] for j in members])
+    col = torch.cat([blocks[j][1] + (area_offsets[j] - base) for j in members])
+    val = torch.cat([blocks[j][2] for j in members])
+    order = torch.sort(row * total + col).indices
+    return row[order], col[order], val[order], total

@@ -262,19 +262,9 @@ def compact_exchange(env, adj_parts, stages, owner_packs=True):
     plans, plan_slices, plan_last = [], [], []
     first = 0
     for count in group_sizes(len(kept), env.stage_group):
-        members = range(first, first + count)
-        base = lay['area_offsets'][first]
-        rows_total = sum(lay['stage_rows'][j] for j in members)
-        if count == 1:
-            row, col, val, _ = blocks[first]
-        else:
-            row = torch.cat([blocks[j][0] for j in members])
-            col = torch.cat([blocks[j][1] + (lay['area_offsets'][j] - base) for j in members])
-            val = torch.cat([blocks[j][2] for j in members])
-            order = torch.sort(row * rows_total + col).indices        # row-major, inside a row ascending (arrival, column)
-            row, col, val = row[order], col[order], val[order]
+        row, col, val, rows_total = schedule.join_packed_blocks(blocks, lay['area_offsets'], first, count)
         plans.append(spmm_cpp.SpmmPlan(row.to(torch.int32), col.to(torch.int32).contiguous(), val.contiguous(), n, rows_total))
-        plan_slices.append((base, rows_total))
+        plan_slices.append((lay['area_offsets'][first], rows_total))
         plan_last.append(first + count - 1)
         first += count
     ex = dict(own=own, remote=kept, plans=plans, plan_slices=plan_slices, plan_last=plan_last, packs=packs, lists=lists,

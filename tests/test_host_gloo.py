@@ -223,6 +223,43 @@ def test_compact_peer_loop_bookkeeping_simulated_on_the_host(P):
         assert np.allclose(z, want, rtol=1e-12, atol=1e-12)
 
 
+@pytest.mark.parametrize('P,spec', [(4, 3), (8, (4, 2, 1)), (8, 7), (5, (2, 1))])
+def test_joined_arrivals_of_the_compact_loop_on_the_host(P, spec):
+    """Arrivals joined into fewer products (stage_group as a size list): the joined block, multiplied by the group's slice
+    of the landing area, adds exactly what the member blocks add one by one, and its entries are in row-major,
+    (arrival, column) order."""
+    from dist_utils import schedule
+    from models.gcn import group_sizes
+    rng = np.random.default_rng(100 + P)
+    n, F, me = 29, 4, 1
+    stages = schedule.stages(me, P, 1)
+    _, remote = schedule.pull_order(stages, me, P)
+    blocks, dense, rows_of = [], [], []
+    for i in remote:
+        a = (rng.random((n, n)) < 0.08) * rng.standard_normal((n, n))
+        touched = np.flatnonzero(np.abs(a).sum(axis=0))
+        if touched.size == 0:
+            continue
+        r, c = np.nonzero(a[:, touched])
+        blocks.append((torch.from_numpy(r), torch.from_numpy(c), torch.from_numpy(a[:, touched][r, c]), int(touched.size)))
+        dense.append(a[:, touched])
+        rows_of.append(int(touched.size))
+    offsets = [sum(rows_of[:j]) for j in range(len(rows_of))]
+    area = rng.standard_normal((sum(rows_of), F))
+    want = sum(d @ area[o:o + k] for d, o, k in zip(dense, offsets, rows_of))
+    got, first = np.zeros((n, F)), 0
+    for count in group_sizes(len(blocks), spec):
+        row, col, val, total = schedule.join_packed_blocks(blocks, offsets, first, count)
+        assert total == sum(rows_of[first:first + count])
+        keys = (row * total + col).numpy()
+        assert np.all(np.diff(keys) > 0)                                   # sorted, no duplicates
+        joined = np.zeros((n, total))
+        joined[row.numpy(), col.numpy()] = val.numpy()
+        got += joined @ area[offsets[first]:offsets[first] + total]
+        first += count
+    assert first == len(blocks) and np.allclose(got, want, rtol=1e-12, atol=1e-12)
+
+
 def test_group_sizes_of_the_compact_loop():
     from models.gcn import group_sizes
     assert group_sizes(7, 1) == [1] * 7 and group_sizes(7, 3) == [3, 3, 1] and group_sizes(7, (4, 2, 1)) == [4, 2, 1]
