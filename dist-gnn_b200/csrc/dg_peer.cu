@@ -303,15 +303,10 @@ int peer_loop(dg_comm* comm, dg_comm* row_comm, const PeerPacks& packs, int32_t 
     if (timed) DG_CUDA(cudaEventRecord(comm->t_begin, compute));
     if (n_products == 0 && count) DG_CUDA(cudaMemsetAsync(z, 0, count * sizeof(float), compute));
     const int b = (int)(comm->peer_loops & 1);
-    // This rank's block goes where its peers can read it; everything queued so far on the compute stream (the producer of
-    // x_local) comes first.
-    static const bool pack_on_side = [] { const char* e = getenv("DG_PACK_SIDE"); return e && e[0] == '1'; }();   // EXPERIMENT
-    cudaStream_t pack_stream = compute;
-    if (packed && pack_on_side) {
-        DG_CUDA(cudaEventRecord(comm->ev_input, compute));
-        DG_CUDA(cudaStreamWaitEvent(comm->side, comm->ev_input, 0));
-        pack_stream = comm->side;
-    }
+    // this rank's block goes where its peers can read it; everything queued so far on the compute stream comes first.
+    // (Packing on the side stream instead, beside the rank's own product, was measured neutral on 2 and 4 GPUs and 3 % slower
+    // on 8 - the products slow down by more than the pack no longer costs in front of them - and a warp-per-row pack kernel
+    // was no faster.)
     if (packed) {
         for (int q = 0; q < packs.n_packs && count; ++q) {
             if (packs.counts[q] == 0) continue;
@@ -319,19 +314,17 @@ int peer_loop(dg_comm* comm, dg_comm* row_comm, const PeerPacks& packs, int32_t 
             const int64_t total = packs.counts[q] * (int64_t)(F % 4 == 0 ? F / 4 : F);
             const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
             if (F % 4 == 0 && (reinterpret_cast<uintptr_t>(x_local) & 15) == 0)
-                k_pack_rows_v4<<<grid, 256, 0, pack_stream>>>(reinterpret_cast<const float4*>(x_local), F / 4, packs.rows[q], packs.counts[q], F / 4,
-                                                              reinterpret_cast<float4*>(dst));
+                k_pack_rows_v4<<<grid, 256, 0, compute>>>(reinterpret_cast<const float4*>(x_local), F / 4, packs.rows[q], packs.counts[q], F / 4,
+                                                          reinterpret_cast<float4*>(dst));
             else
-                k_pack_rows<<<grid, 256, 0, pack_stream>>>(x_local, F, packs.rows[q], packs.counts[q], F, dst);
+                k_pack_rows<<<grid, 256, 0, compute>>>(x_local, F, packs.rows[q], packs.counts[q], F, dst);
         }
         DG_CUDA(cudaGetLastError());
     } else if (count) {
         DG_CUDA(cudaMemcpyAsync(comm->peer_send[b], x_local, count * sizeof(float), cudaMemcpyDeviceToDevice, compute));
     }
-    if (pack_stream == compute) {
-        DG_CUDA(cudaEventRecord(comm->ev_input, compute));
-        DG_CUDA(cudaStreamWaitEvent(comm->side, comm->ev_input, 0));
-    }
+    DG_CUDA(cudaEventRecord(comm->ev_input, compute));
+    DG_CUDA(cudaStreamWaitEvent(comm->side, comm->ev_input, 0));
     DG_NCCL(ncclAllReduce(comm->peer_token, comm->peer_token, 1, ncclFloat, ncclMax, comm->comm, comm->side));
     DG_CUDA(cudaEventRecord(comm->ev_barrier, comm->side));
     const int lanes = 2;                                          // pieces of a block in flight side by side (measured best of 1, 2, 4)

@@ -46,24 +46,21 @@ class DistEnv:
         #                of the rows at 8 ranks on the benchmark graph): the owner packs them per reader, the reader copies.
         # 'peer_gather':  the same rows, gathered by the reader out of the owner's whole block with a small pull kernel; the
         #                owners pack nothing and nothing is exchanged beforehand.
-        # Default: peer_compact for 1D (2 GPUs: 37.8 ms against 38.6 for peer_copy and 48.2 for 'reference'; peer_copy at 8
-        # GPUs: 25.4 against 27.4, with 0.8-0.9 of the transfer hidden), reference for 1.5D (peer copies were slower there).
+        # Default: peer_compact for 1D (8 GPUs: 15.5 ms per epoch on the benchmark graph against 19.5 for peer_gather; the
+        # broadcast loops and peer_copy were 25-30 ms with earlier kernels), reference for 1.5D (peer copies were slower there).
         default_order = 'peer_compact' if rep == 1 else 'reference'
         self.stage_order = stage_order if stage_order is not None else os.environ.get('DIST_GNN_STAGE_ORDER', default_order)
         if self.stage_order not in ('reference', 'local_first', 'feature_chunks', 'peer_copy', 'peer_compact', 'peer_gather'):
             raise ValueError(f'unknown stage order {self.stage_order!r}')
-        # Stages fused into one product (1 = stage by stage, as the reference).  Peer copies and 1.5D run stage by stage;
-        # the broadcast loop of 1D is fastest with two products per distributed SpMM (half of the stages each): longer
-        # rows per product and one read-modify-write of z instead of P-1, while the second half travels under the first.
+        # Stages fused into one product (1 = stage by stage, as the reference); the defaults and the measurements behind
+        # them are in schedule.default_stage_group.
         chosen = stage_group if stage_group is not None else os.environ.get('DIST_GNN_STAGE_GROUP')
         if chosen is not None:
             # an integer, or for 'peer_compact' a list of group sizes such as "4,2,1" (arrivals per product, in pull order)
             sizes = [max(1, int(v)) for v in str(chosen).replace('(', '').replace(')', '').replace('[', '').replace(']', '').split(',') if v.strip()]
             self.stage_group = sizes[0] if len(sizes) == 1 else tuple(sizes)
-        elif self.stage_order == 'reference' and rep == 1:
-            self.stage_group = max(1, (len(self.stages()) + 1) // 2)
         else:
-            self.stage_group = 1
+            self.stage_group = schedule.default_stage_group(self.stage_order, rep, len(self.stages()))
         self.chunk_width = int(os.environ.get('DIST_GNN_CHUNK_WIDTH', 64))
         DistEnv.env = self
 
@@ -190,7 +187,7 @@ class DistEnv:
             if self.rank == 0:
                 print(f"[dist-gnn] peer-copy stage order unavailable ({why if not ok else 'on a peer'}); using NCCL broadcasts", flush=True)
             self.stage_order = 'reference'
-            self.stage_group = max(1, (len(self.stages()) + 1) // 2) if self.rep == 1 else 1
+            self.stage_group = schedule.default_stage_group('reference', self.rep, len(self.stages()))
             return False
         dist.barrier(group, device_ids=[self.device.index])
         return True

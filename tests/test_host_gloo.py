@@ -260,6 +260,17 @@ def test_joined_arrivals_of_the_compact_loop_on_the_host(P, spec):
     assert first == len(blocks) and np.allclose(got, want, rtol=1e-12, atol=1e-12)
 
 
+def test_default_stage_groups():
+    from dist_utils import schedule
+    from models.gcn import group_sizes
+    assert schedule.default_stage_group('reference', 1, 8) == 4 and schedule.default_stage_group('reference', 2, 2) == 1
+    assert schedule.default_stage_group('peer_compact', 1, 2) == 1 and schedule.default_stage_group('peer_compact', 1, 4) == 1
+    assert schedule.default_stage_group('peer_compact', 1, 8) == (1, 1, 1, 2, 2)
+    assert group_sizes(7, schedule.default_stage_group('peer_compact', 1, 8)) == [1, 1, 1, 2, 2]
+    assert group_sizes(15, schedule.default_stage_group('peer_gather', 1, 16)) == [1] * 11 + [2, 2]
+    assert schedule.default_stage_group('peer_copy', 1, 8) == 1 and schedule.default_stage_group('peer_compact', 2, 8) == 1
+
+
 def test_group_sizes_of_the_compact_loop():
     from models.gcn import group_sizes
     assert group_sizes(7, 1) == [1] * 7 and group_sizes(7, 3) == [3, 3, 1] and group_sizes(7, (4, 2, 1)) == [4, 2, 1]
