@@ -46,7 +46,7 @@ class DistEnv:
         #                of the rows at 8 ranks on the benchmark graph): the owner packs them per reader, the reader copies.
         # 'peer_gather':  the same rows, gathered by the reader out of the owner's whole block with a small pull kernel; the
         #                owners pack nothing and nothing is exchanged beforehand.
-        # Default: peer_compact for 1D (8 GPUs: 15.5 ms per epoch on the benchmark graph against 19.5 for peer_gather; the
+        # Default: peer_compact for 1D (8 GPUs: 15.7 ms per epoch on the benchmark graph against 19.5 for peer_gather; the
         # broadcast loops and peer_copy were 25-30 ms with earlier kernels), reference for 1.5D (peer copies were slower there).
         default_order = 'peer_compact' if rep == 1 else 'reference'
         self.stage_order = stage_order if stage_order is not None else os.environ.get('DIST_GNN_STAGE_ORDER', default_order)

@@ -120,14 +120,16 @@ def default_stage_group(stage_order, rep, n_stages):
     """Stages (or arrivals) per product when the caller does not say.
     'reference', 1D: two products per distributed SpMM (half of the stages each): longer rows per product and one
         read-modify-write of the result instead of P-1, while the second half travels under the first.
-    'peer_compact' / 'peer_gather', 1D, 8 ranks or more: one product per arrival, the last four arrivals joined in pairs
-        (1,1,1,2,2 at 8 ranks).  By then the products run behind the transfers, so the joined blocks do not wait, and two
-        passes over the result are saved: 15.5 ms per epoch on the benchmark graph against 16.2 (all single), 15.7
-        (1,1,1,1,1,2), 15.8 (1,1,1,1,3 and 1,1,2,3), 16.6 (4,2,1).  With fewer ranks the products dominate and waiting for
-        a joined arrival costs what the join saves (4 ranks: 22.5 / 23.3 / 25.2 ms for 1 / 2,1 / 3).
+    'peer_compact' / 'peer_gather', 1D, 8 ranks or more: one product per arrival, the last two arrivals joined
+        (1,1,1,1,1,2 at 8 ranks).  By then the products run behind the transfers, so the joined block does not wait, and
+        a pass over the result is saved: 15.7 ms per epoch on the benchmark graph with 0.77 of the transfer hidden at
+        width 256, against 16.2 ms / 0.79 (all single), 15.5-15.7 ms / 0.70 (1,1,1,2,2), 15.8 ms / 0.54-0.61 (1,1,1,1,3 and
+        1,1,2,3), 16.6 ms / 0.38 (4,2,1): joining more keeps shaving product time but exposes the transfer.  With fewer
+        ranks the products dominate and waiting for a joined arrival costs what the join saves (4 ranks: 22.5 / 23.3 /
+        25.2 ms for 1 / 2,1 / 3).
     Everything else: stage by stage."""
     if stage_order == 'reference' and rep == 1:
         return max(1, (n_stages + 1) // 2)
     if stage_order in ('peer_compact', 'peer_gather') and rep == 1 and n_stages >= 8:
-        return tuple([1] * (n_stages - 1 - 4) + [2, 2])
+        return tuple([1] * (n_stages - 1 - 2) + [2])
     return 1

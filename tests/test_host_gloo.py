@@ -265,9 +265,9 @@ def test_default_stage_groups():
     from models.gcn import group_sizes
     assert schedule.default_stage_group('reference', 1, 8) == 4 and schedule.default_stage_group('reference', 2, 2) == 1
     assert schedule.default_stage_group('peer_compact', 1, 2) == 1 and schedule.default_stage_group('peer_compact', 1, 4) == 1
-    assert schedule.default_stage_group('peer_compact', 1, 8) == (1, 1, 1, 2, 2)
-    assert group_sizes(7, schedule.default_stage_group('peer_compact', 1, 8)) == [1, 1, 1, 2, 2]
-    assert group_sizes(15, schedule.default_stage_group('peer_gather', 1, 16)) == [1] * 11 + [2, 2]
+    assert schedule.default_stage_group('peer_compact', 1, 8) == (1, 1, 1, 1, 1, 2)
+    assert group_sizes(7, schedule.default_stage_group('peer_compact', 1, 8)) == [1, 1, 1, 1, 1, 2]
+    assert group_sizes(15, schedule.default_stage_group('peer_gather', 1, 16)) == [1] * 13 + [2]
     assert schedule.default_stage_group('peer_copy', 1, 8) == 1 and schedule.default_stage_group('peer_compact', 2, 8) == 1
 
 
