@@ -192,7 +192,9 @@ class DistEnv:
         dist.barrier(group, device_ids=[self.device.index])
         return True
 
-    def shutdown(self):
+    def shutdown(self, keep_process_group=False):
+        """Closes the peer mappings and the library communicators; keep_process_group=True leaves torch.distributed
+        initialised so that another DistEnv (another partition layout) can follow in the same process."""
         comms = list({id(c): c for c in (self.row_comm, self.col_comm, self.comm) if c is not None}.values())
         if any(c.peer_capacity() > 0 for c in comms):
             torch.cuda.synchronize(self.device)
@@ -203,6 +205,7 @@ class DistEnv:
         for c in comms:
             c.destroy()
         self.comm = self.col_comm = self.row_comm = None
-        if dist.is_initialized():
+        self._recv = {}
+        if dist.is_initialized() and not keep_process_group:
             dist.destroy_process_group()
         DistEnv.env = None

@@ -307,6 +307,12 @@ def ordered_products(env, adj_parts, stages, x, rotate=False):
 _group_plan_cache = {}
 
 
+def drop_cached_plans():
+    """Forgets the joined plans and exchange tables kept per graph (they hold the graph's blocks alive)."""
+    _compact_cache.clear()
+    _group_plan_cache.clear()
+
+
 def group_plans(adj_parts, parts, group):
     """Plans of the stage loop's products.  group = 1: one per column block, as the reference multiplies them.
     group = k: the blocks of k consecutive stages are joined side by side into one n x (k*n) block (entries stay in

@@ -86,6 +86,43 @@ def _run(world, rep, port):
     return z, [np.load(os.path.join(out_dir, f'rank{r}.npz')) for r in range(world)]
 
 
+
+def _two_layouts_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port), DIST_GNN_LOG_ROOT=out_dir)
+    for p in (ROOT, PKG):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import torch.distributed as dist
+    from dist_utils import DistEnv
+    torch.set_num_threads(1)
+    first = DistEnv(rank, world, 'gloo')
+    w = torch.full((2,), float(rank + 1))
+    first.all_reduce_sum(w)
+    stages_1d = len(first.stages())
+    first.shutdown(keep_process_group=True)
+    assert dist.is_initialized() and DistEnv.env is None
+    second = DistEnv(rank, world, 'gloo', rep=2)            # another layout on the same process group
+    v = torch.full((2,), float(rank + 1))
+    second.all_reduce_sum(v)                                # column group: the ranks with the same replica index
+    second.barrier_all()
+    rec = dict(w=w.numpy(), v=v.numpy(), stages=np.array([stages_1d, len(second.stages())]))
+    second.shutdown()
+    assert not dist.is_initialized()
+    np.savez(os.path.join(out_dir, f'rank{rank}.npz'), **rec)
+
+
+def test_a_second_layout_follows_in_the_same_processes():
+    """bench.py measures the 1.5D configuration after the 1D one without a new rendezvous."""
+    import torch.multiprocessing as mp
+    out_dir = tempfile.mkdtemp(prefix='dg_gloo_two_')
+    mp.spawn(_two_layouts_worker, (4, 29631, out_dir), nprocs=4, join=True)
+    recs = [np.load(os.path.join(out_dir, f'rank{r}.npz')) for r in range(4)]
+    for r, rec in enumerate(recs):
+        assert rec['w'].tolist() == [10.0, 10.0]                                   # 1 + 2 + 3 + 4 over the world
+        assert rec['v'].tolist() == ([4.0, 4.0] if r % 2 == 0 else [6.0, 6.0])      # ranks {0, 2} and {1, 3}
+        assert rec['stages'].tolist() == [4, 1]                                       # R = 2 blocks, each replica takes one
+
+
 def _oracle_parts(z, R):
     from oracle import ref_graph
     n = int(z['in/meta'][0])
