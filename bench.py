@@ -10,7 +10,8 @@ graph, labels and split are regenerated from a seed on every rank (integer hash,
 total problem is split over N ranks, so scaling is "strong".  Rank 0 prints ONE JSON line.  Beside the contract's keys it
 carries `parity` (the distributed product of the active schedule against a float64 evaluation of sampled rows; the run
 exits non-zero above 1e-5), `reuse` (the same epochs with the constant first-layer product kept), `comm` (N > 1) and
-`run` (schedule, median epoch).  `--impl reference` runs the unmodified reference from baseline/_ref over gloo.
+`run` (schedule, median epoch).  A default 8-GPU run also carries `config3`: the same graph under the 1.5D partition (c = 2,
+4 layers), measured afterwards by the same processes.  `--impl reference` runs the unmodified reference from baseline/_ref over gloo.
 """
 import argparse
 import json
