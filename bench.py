@@ -449,8 +449,18 @@ def sample_config(cfg, divisor):
 def config_block(cfg, args, world):
     """The `config` object, the same in both arms."""
     return {'workload': describe(cfg, args, world), 'partition': '1d' if args.rep == 1 else f'1.5d(c={args.rep})', 'seed': args.seed,
-            'vertex_permutation': not args.no_permute,
-            'cache': 'inputs larger than L2 (adjacency + operands are GBs per rank); no flush'}
+            'vertex_permutation': not args.no_permute, 'cache': cache_note(cfg, args, world)}
+
+
+def cache_note(cfg, args, world):
+    """Whether one rank's share of the step's inputs exceeds the 126 MB L2 (no flush is made between timed steps)."""
+    blocks = max(1, world // max(1, args.rep))
+    stored = (cfg['directed_edges'] + cfg['num_nodes']) // blocks                      # entries of a rank's row block
+    widest = max(cfg['feat_dim'], cfg['hidden'])
+    per_rank = stored * 12 + 2 * (cfg['num_nodes'] // blocks) * widest * 4             # ids + values, an operand and a result
+    if per_rank > 2 * 126e6:
+        return f'inputs larger than L2 ({per_rank / 1e9:.2f} GB of adjacency + widest operand and result per rank against 126 MB); no flush'
+    return f'inputs of {per_rank / 1e6:.0f} MB per rank fit in the 126 MB L2 and no flush is made: a plumbing workload, not a benchmark configuration'
 
 
 def _reference_worker(rank, workdir, parts, name, warmup, steps, threads, port):
