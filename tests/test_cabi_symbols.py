@@ -56,3 +56,40 @@ def test_product_modules_do_not_import_the_oracle():
                 text = open(os.path.join(folder, f)).read()
                 assert not re.search(r'^\s*(from|import)\s+oracle\b|oracle[/.](ref_|spmm_ref|_build|_ref)', text, flags=re.M), \
                     f'{f} reaches into the oracle'
+
+
+def _top_level_arguments(text, start):
+    """Number of arguments of the call whose opening bracket ends at text[start - 1]."""
+    depth, commas, empty, i = 1, 0, True, start
+    while depth:
+        ch = text[i]
+        if ch in '([{':
+            depth += 1
+        elif ch in ')]}':
+            depth -= 1
+        elif ch == ',' and depth == 1:
+            commas += 1
+        if depth and not ch.isspace():
+            empty = False
+        i += 1
+    return 0 if empty else commas + 1
+
+
+def test_c_examples_of_the_integration_guide_match_the_header():
+    """Every dg_* call in the guide's C / C++ snippets passes as many arguments as the header's prototype takes."""
+    header = open(os.path.join(ROOT, 'include', 'dist_gnn_b200.h')).read()
+    header = re.sub(r'//[^\n]*', '', re.sub(r'/\*.*?\*/', '', header, flags=re.S))
+    takes = {}
+    for m in re.finditer(r'\b(dg_[a-z0-9_]+)\s*\(([^;{]*?)\)\s*;', header, flags=re.S):
+        inside = m.group(2).strip()
+        takes[m.group(1)] = 0 if inside in ('', 'void') else inside.count(',') + 1
+    guide = open(os.path.join(ROOT, 'INTEGRATION.md')).read()
+    snippets = re.findall(r'```(?:c|cpp)\n(.*?)```', guide, flags=re.S)
+    seen = 0
+    for snippet in snippets:
+        snippet = re.sub(r'/\*.*?\*/', '', snippet, flags=re.S)
+        for m in re.finditer(r'\b(dg_[a-z0-9_]+)\s*\(', snippet):
+            assert m.group(1) in takes, f'{m.group(1)} is used in the guide but not declared'
+            assert _top_level_arguments(snippet, m.end()) == takes[m.group(1)], f'{m.group(1)}: argument count differs from the header'
+            seen += 1
+    assert seen >= 15
